@@ -115,6 +115,7 @@ int qspec_moe_route_chosen(const void* h, const float* router_w, int* idx, float
  * qspec_moe_expert_tokens. RELU2: up rows only (weights [E, F, W]), y = max(up h, 0)^2; `limit` is ignored. */
 #define QSPEC_EXPERT_ACT_GATED 0
 #define QSPEC_EXPERT_ACT_RELU2 1
+#define QSPEC_EXPERT_ACT_SILU  2   /* [gate ; up] rows like GATED, y = silu(gate h) * (up h); `limit` is ignored */
 int qspec_moe_expert_tokens_act(const void* h, const void* up, const void* down, const int* idx, void* out, int ntok, int W,
                                 int F, int E, int top, float limit, int act, int dtype, void* stream);
 int qspec_moe_expert_grouped_act(const void* h, const void* up, const void* down, const int* idx, void* out, int ntok, int W,
@@ -172,6 +173,7 @@ typedef struct qspec_window_attn_args {
   const void* v; long long v_slot_stride; int v_row_stride, v_head_stride; int DV;
   const float* sink; const void* gate; int gate_ld;
   void* out; const int* meta; int ntok, H, G, window, cap; float scale;
+  int gate_per_head;   /* 0: gate[t, h * DV + d] as above; 1: one gate per head, gate[t, h] (gate_ld >= H) */
 } qspec_window_attn_args;
 int qspec_seq_window_attention(const qspec_window_attn_args* args, int dtype, void* stream);
 
@@ -197,6 +199,58 @@ int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower,
 /* g[t, :] <- gelu_tanh(g[t, :]) * table[ids[t], col0 : col0 + sd]  (g [ntok, sd], table [V, table_ld]). */
 int qspec_seq_side_gate(void* g, const void* table, const int* ids, int col0, int sd, int table_ld, int V, int ntok, int dtype,
                         void* stream);
+
+/* ---- pre-norm designs with a scaled residual, full-length latent caches, scalar-decay linear attention, sigmoid routers with
+ * expert groups. ---- */
+
+/* Residual sum and the next sublayer's input norm in one launch:
+ *   r = x_in + mult * (sum_p y_w[t, p] * y[t, p, :] + y2_w[t * y2_w_stride] * y2[t, :])      (y NULL: r = x_in; y2 NULL: no such term)
+ *   out = r / sqrt(mean(r^2) + eps) * (w_offset + w)
+ * y_w NULL: ones; y2_w NULL: one. r goes to x_out (float32, may alias x_in, may be NULL), the norm to out (activation type,
+ * may be NULL). y and y2 have element type y_dtype: the activation type or float32. W <= 49152. */
+int qspec_seq_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                            long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
+                            float mult, const float* w, float w_offset, void* out, int ntok, int W, float eps, int y_dtype, int dtype,
+                            void* stream);
+
+/* Rotary pairings: HALVES turns entry i with entry i + rot_dims / 2; INTERLEAVED turns entry 2i with entry 2i + 1. In both the
+ * angle of pair i is pos * inv_freq[i]. */
+#define QSPEC_ROTARY_HALVES 0
+#define QSPEC_ROTARY_INTERLEAVED 1
+/* qspec_seq_latent_prep with the pairing as an argument; q_rank may be 0 (no query latent: qn_w and cq are not read). */
+int qspec_seq_latent_prep_pairing(const void* d, int ld, int q_rank, int kv_rank, int rot_dim, const float* qn_w, const float* kvn_w,
+                                  const float* inv_freq, int rot_dims, int pairing, void* cq, void* cache, int cap, const int* meta,
+                                  int ntok, float eps, int dtype, void* stream);
+/* qspec_seq_rotary with the pairing as an argument. */
+int qspec_seq_rotary_pairing(const void* src, long long src_tok_stride, int src_head_stride, int off, float* dst,
+                             long long dst_tok_stride, int dst_head_stride, int H, int n, int rot_dims, int pairing,
+                             const float* inv_freq, const int* meta, int ntok, int dtype, void* stream);
+
+/* a <- act(a), n elements. */
+#define QSPEC_ACT_RELU2 0
+#define QSPEC_ACT_GELU_ERF 1
+int qspec_seq_act(void* a, long long n, int act, int dtype, void* stream);
+/* out[t, f] = silu(gu[t, f]) * gu[t, F + f]: rows of gu are [gate (F) | up (F)] with leading dimension ld; out [ntok, F]. */
+int qspec_seq_silu_mul(const void* gu, int ld, void* out, int ntok, int F, int dtype, void* stream);
+
+/* Linear attention with one decay per head ("lightning"). Row t of p = [zq (H x D) | zk (H x D) | zv (H x DV) | zg (H x DV)].
+ * q = silu(zq), k = silu(zk), v = silu(zv); per head S <- decay[h] * S + k v^T, o = S^T q; the concatenated heads are
+ * normed together: out[t, :] = o / sqrt(mean over all H * DV of o^2 + eps) * norm_w * sigmoid(zg). state: float32
+ * [slots, H, D, DV], read at a segment's start (zero at position 0), written at its end. scratch: float32 with room for
+ * ntok * H * (DV + 2 D) values. seg_starts as for qspec_seq_hgrn2. D <= 256. */
+int qspec_seq_lightning(const void* p, int ld, const float* decay, const float* norm_w, float* state, float* scratch, void* out,
+                        const int* meta, const int* seg_starts, int nseg, int ntok, int H, int D, int DV, float eps, int dtype,
+                        void* stream);
+
+/* Router with a score function, expert groups and gate rows. z = router_w h (float32; router_w [R + n_extra, W]).
+ * Scores s = softmax(z[0:R]) (score_fn 0) or sigmoid(z[0:R]) (score_fn 1); choice = s + correction (NULL: zeros). The R
+ * experts form n_groups equal groups of neighbours; a group's score is the sum of its group_top largest choice scores; only
+ * experts of the keep_groups best groups can be chosen (n_groups <= 1: no limit). The `top` largest remaining choices (lowest
+ * index among equals) -> idx, weight = scale * s of the chosen. extra[t, x] = sigmoid(z[R + x]) for the n_extra gate rows
+ * (extra float32 [ntok, extra_ld]). R + n_extra <= 1024, top <= 32. */
+int qspec_moe_route_grouped(const void* h, const float* router_w, const float* correction, int* idx, float* weight, float* extra,
+                            int extra_ld, int ntok, int W, int R, int top, int score_fn, int n_groups, int keep_groups,
+                            int group_top, float scale, int n_extra, int dtype, void* stream);
 
 /* Arg max per row of float32 / bfloat16 logits [rows, V] (lowest index among equal maxima): int64 out. */
 int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,

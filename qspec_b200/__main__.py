@@ -30,11 +30,13 @@ def _generate(argv) -> int:
     from .build import build_library, build_seq_library
     arch = registry.architecture_of(registry.read_config(args.model))
     build_seq_library()
-    if arch not in ("Mutusun", "Pitudra"):
+    if arch not in ("Mutusun", "Pitudra", "Repepel"):
         build_library()
     from .scheduler import Scheduler
-    model = registry.load_model(args.model, dtype=args.dtype, n_slots=args.slots, max_step_tokens=args.step_tokens)
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt]
+    # models whose cache grows with the sequence size it for the longest request
+    model = registry.load_model(args.model, dtype=args.dtype, n_slots=args.slots, max_step_tokens=args.step_tokens,
+                                max_seq_tokens=max(len(p) for p in prompts) + args.max_new_tokens)
     outs = Scheduler(model, prefill_portion=args.prefill_portion).generate(prompts, args.max_new_tokens, eos=args.eos)
     for p, o in zip(prompts, outs):
         print(json.dumps({"prompt": p, "tokens": o}))

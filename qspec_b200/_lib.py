@@ -149,6 +149,18 @@ SEQ_SIGNATURES = {
     "qspec_seq_hgrn2": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "qspec_seq_side_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "qspec_seq_residual_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                        c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p]),
+    "qspec_seq_latent_prep_pairing": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                              c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_rotary_pairing": (c_int, [c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                         c_void_p, c_int, c_int, c_void_p]),
+    "qspec_seq_act": (c_int, [c_void_p, c_ll, c_int, c_int, c_void_p]),
+    "qspec_seq_silu_mul": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "qspec_seq_lightning": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                    c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_moe_route_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
 }
 
 
@@ -160,7 +172,7 @@ class WindowAttnArgs(ctypes.Structure):
                 ("v", c_void_p), ("v_slot_stride", c_ll), ("v_row_stride", c_int), ("v_head_stride", c_int), ("DV", c_int),
                 ("sink", c_void_p), ("gate", c_void_p), ("gate_ld", c_int),
                 ("out", c_void_p), ("meta", c_void_p), ("ntok", c_int), ("H", c_int), ("G", c_int), ("window", c_int),
-                ("cap", c_int), ("scale", c_float)]
+                ("cap", c_int), ("scale", c_float), ("gate_per_head", c_int)]
 
 _lib = None
 _seq_lib = None

@@ -536,15 +536,22 @@ __global__ void __launch_bounds__(256) relu2_kernel(T* __restrict__ a, long long
   }
 }
 
-// Router: one CTA of 128 threads per token. Dot products by warp, then softmax and top-k by one warp.
+// Router: one CTA of 128 threads per token. Dot products by warp, then scores (softmax or sigmoid), group limits and top-k
+// by one warp. The last n_extra rows of the router matrix are gate rows: their sigmoid goes to `extra`.
+struct RouteOpts {
+  int score_fn, n_groups, keep_groups, group_top, n_extra, extra_ld;
+  float scale;
+  float* extra;
+};
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float* __restrict__ corr, int* __restrict__ idx,
-             float* __restrict__ weight, int W, int R, int top, int chosen_only) {
+             float* __restrict__ weight, int W, int RE, int top, int chosen_only, RouteOpts ro) {
   pdl_enter();
-  extern __shared__ float sm_rt[];            // z [R] | choice [R]
+  extern __shared__ float sm_rt[];            // z [R + gate rows] | choice [R] | group scores
+  const int R = RE - ro.n_extra;              // the dot products cover the gate rows too; everything after them the experts only
   float* z = sm_rt;
-  float* ch = sm_rt + R;
+  float* ch = sm_rt + RE;
   const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* hp = h + (size_t)i * W;
   // four elements per lane and load where the rows allow it, four such loads in flight: the dot products are short and
@@ -554,7 +561,7 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
     // four router rows of a warp at a time (rows warp, warp + 4, warp + 8, warp + 12 of a group of 16): the token's row is
     // loaded once per step and four weight loads are in flight; every row keeps its own four partial sums, so the result
     // is the one of a row-by-row loop
-    for (int r0 = warp; r0 < R; r0 += 16) {
+    for (int r0 = warp; r0 < RE; r0 += 16) {
       float a4[4][4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) a4[u][0] = a4[u][1] = a4[u][2] = a4[u][3] = 0.f;
@@ -564,7 +571,7 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int r = r0 + 4 * u;
-          if (r < R) {
+          if (r < RE) {
             const float4 wv = *reinterpret_cast<const float4*>(rw + (size_t)r * W + c);
             a4[u][0] += wv.x * hv.v[0]; a4[u][1] += wv.y * hv.v[1]; a4[u][2] += wv.z * hv.v[2]; a4[u][3] += wv.w * hv.v[3];
           }
@@ -574,11 +581,11 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
       for (int u = 0; u < 4; ++u) {
         const int r = r0 + 4 * u;
         const float acc = warp_xor_sum((a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]));
-        if (r < R && lane == 0) z[r] = acc;
+        if (r < RE && lane == 0) z[r] = acc;
       }
     }
   } else {
-    for (int r = warp; r < R; r += 4) {
+    for (int r = warp; r < RE; r += 4) {
       const float* wr = rw + (size_t)r * W;
       float acc = 0.f;
       for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
@@ -617,21 +624,63 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
       for (int k = 0; k < top; ++k) weight[(size_t)i * top + k] /= sum;
     return;
   }
-  float mx = -INFINITY;
-  for (int r = lane; r < R; r += 32) mx = fmaxf(mx, z[r]);
-  mx = warp_xor_max(mx);
-  float sum = 0.f;
-  for (int r = lane; r < R; r += 32) {
-    const float e = expf(z[r] - mx);
-    z[r] = e;
-    sum += e;
-  }
-  sum = warp_xor_sum(sum);
-  for (int r = lane; r < R; r += 32) {
-    z[r] = z[r] / sum;
-    ch[r] = z[r] + corr[r];
+  for (int x = lane; x < ro.n_extra; x += 32) ro.extra[(size_t)i * ro.extra_ld + x] = 1.0f / (1.0f + expf(-z[R + x]));
+  if (ro.score_fn == 1) {
+    for (int r = lane; r < R; r += 32) {
+      z[r] = 1.0f / (1.0f + expf(-z[r]));
+      ch[r] = z[r] + (corr ? corr[r] : 0.f);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int r = lane; r < R; r += 32) mx = fmaxf(mx, z[r]);
+    mx = warp_xor_max(mx);
+    float sum = 0.f;
+    for (int r = lane; r < R; r += 32) {
+      const float e = expf(z[r] - mx);
+      z[r] = e;
+      sum += e;
+    }
+    sum = warp_xor_sum(sum);
+    for (int r = lane; r < R; r += 32) {
+      z[r] = z[r] / sum;
+      ch[r] = z[r] + (corr ? corr[r] : 0.f);
+    }
   }
   __syncwarp();
+  if (ro.n_groups > 1) {
+    // a group's score: the sum of its group_top largest choice scores (a lane per group); then every group counts the
+    // groups ahead of it (larger score, or equal score and lower index) and drops out when keep_groups or more are
+    float* gs = ch + R;
+    const int size = R / ro.n_groups;
+    for (int g = lane; g < ro.n_groups; g += 32) {
+      const float* c = ch + g * size;
+      float acc = 0.f, last = INFINITY;
+      int last_i = -1;
+      for (int k = 0; k < ro.group_top && k < size; ++k) {     // k-th largest: the largest entry after (last, last_i) in the order
+        float bv = -INFINITY;
+        int bi = -1;
+        for (int e = 0; e < size; ++e) {
+          const float v = c[e];
+          const bool after = v < last || (v == last && e > last_i);
+          if (after && (bi < 0 || v > bv)) { bv = v; bi = e; }
+        }
+        if (bi < 0) break;
+        acc += bv;
+        last = bv;
+        last_i = bi;
+      }
+      gs[g] = acc;
+    }
+    __syncwarp();
+    for (int g = lane; g < ro.n_groups; g += 32) {
+      const float mine = gs[g];
+      int ahead = 0;
+      for (int o = 0; o < ro.n_groups; ++o) ahead += (gs[o] > mine || (gs[o] == mine && o < g)) ? 1 : 0;
+      if (ahead >= ro.keep_groups)
+        for (int e = 0; e < size; ++e) ch[g * size + e] = -INFINITY;
+    }
+    __syncwarp();
+  }
   for (int k = 0; k < top; ++k) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -646,7 +695,7 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
     if (bi >= R) bi = 0;                                      // NaN scores: still a valid index
     if (lane == 0) {
       idx[(size_t)i * top + k] = bi;
-      weight[(size_t)i * top + k] = z[bi];
+      weight[(size_t)i * top + k] = z[bi] * ro.scale;
       ch[bi] = -INFINITY;
     }
     __syncwarp();
@@ -696,9 +745,14 @@ expert_tokens_kernel(const T* __restrict__ h, const T* __restrict__ gate_up, con
     au = warp_xor_sum(au);
     if (lane == 0) {
       // the projections leave the matrix unit in the activation type
-      const float gq = fminf(to_f(from_f<T>(ag)), limit);
-      const float uq = fminf(fmaxf(to_f(from_f<T>(au)), -limit), limit);
-      sy[f] = to_f(from_f<T>(gq * (1.0f / (1.0f + expf(-1.702f * gq))) * (uq + 1.0f)));
+      if (act == QSPEC_EXPERT_ACT_SILU) {
+        const float gq = to_f(from_f<T>(ag)), uq = to_f(from_f<T>(au));
+        sy[f] = to_f(from_f<T>(gq / (1.0f + expf(-gq)) * uq));
+      } else {
+        const float gq = fminf(to_f(from_f<T>(ag)), limit);
+        const float uq = fminf(fmaxf(to_f(from_f<T>(au)), -limit), limit);
+        sy[f] = to_f(from_f<T>(gq * (1.0f / (1.0f + expf(-1.702f * gq))) * (uq + 1.0f)));
+      }
     }
   }
   __syncthreads();
@@ -990,21 +1044,36 @@ extern "C" int qspec_seq_relu2(void* a, long long n, int dtype, void* stream) {
 }
 
 static int route_any(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W, int R, int top,
-                     int chosen_only, int dtype, void* stream) {
-  QSPEC_REQUIRE(h && router_w && (correction || chosen_only) && idx && weight, QSPEC_ERR_INVALID_ARG, "moe_route: null pointer");
-  QSPEC_REQUIRE(ntok >= 0 && W > 0 && R > 0 && R <= 1024 && top >= 1 && top <= 32 && top <= R, QSPEC_ERR_UNSUPPORTED,
-                "moe_route: %d router outputs (<= 1024), top %d (<= 32)", R, top);
+                     int chosen_only, int dtype, void* stream, const RouteOpts* opts = nullptr) {
+  RouteOpts ro = {0, 1, 1, 1, 0, 0, 1.0f, nullptr};
+  if (opts) ro = *opts;
+  QSPEC_REQUIRE(h && router_w && (correction || chosen_only || opts) && idx && weight, QSPEC_ERR_INVALID_ARG, "moe_route: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && R > 0 && R + ro.n_extra <= 1024 && top >= 1 && top <= 32 && top <= R, QSPEC_ERR_UNSUPPORTED,
+                "moe_route: %d router outputs (<= 1024), top %d (<= 32)", R + ro.n_extra, top);
+  QSPEC_REQUIRE(ro.n_extra >= 0 && (ro.n_extra == 0 || (ro.extra && ro.extra_ld >= ro.n_extra)), QSPEC_ERR_INVALID_ARG, "moe_route: gate rows without an output");
+  QSPEC_REQUIRE(ro.n_groups >= 1 && R % ro.n_groups == 0 && ro.keep_groups >= 1 && ro.keep_groups <= ro.n_groups && ro.group_top >= 1 &&
+                    top <= ro.keep_groups * (R / ro.n_groups),
+                QSPEC_ERR_INVALID_ARG, "moe_route: %d groups (keep %d) of %d experts, top %d", ro.n_groups, ro.keep_groups, R, top);
   SEQ_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
-  const size_t smem = (size_t)2 * R * sizeof(float);
+  const int RE = R + ro.n_extra;
+  const size_t smem = (size_t)(RE + R + ro.n_groups) * sizeof(float);
   if (dtype == QSPEC_DTYPE_F32)
     launch_pdl(route_kernel<float>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const float*)h, router_w, correction, idx,
-               weight, W, R, top, chosen_only);
+               weight, W, RE, top, chosen_only, ro);
   else
     launch_pdl(route_kernel<__nv_bfloat16>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)h, router_w,
-               correction, idx, weight, W, R, top, chosen_only);
+               correction, idx, weight, W, RE, top, chosen_only, ro);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
+}
+
+extern "C" int qspec_moe_route_grouped(const void* h, const float* router_w, const float* correction, int* idx, float* weight, float* extra,
+                                       int extra_ld, int ntok, int W, int R, int top, int score_fn, int n_groups, int keep_groups,
+                                       int group_top, float scale, int n_extra, int dtype, void* stream) {
+  QSPEC_REQUIRE(score_fn == 0 || score_fn == 1, QSPEC_ERR_INVALID_ARG, "moe_route_grouped: score function %d", score_fn);
+  RouteOpts ro = {score_fn, n_groups < 1 ? 1 : n_groups, n_groups < 1 ? 1 : keep_groups, group_top, n_extra, extra_ld, scale, extra};
+  return route_any(h, router_w, correction, idx, weight, ntok, W, R, top, 0, dtype, stream, &ro);
 }
 
 extern "C" int qspec_moe_route(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W,
@@ -1019,7 +1088,8 @@ extern "C" int qspec_moe_route_chosen(const void* h, const float* router_w, int*
 
 extern "C" int qspec_moe_expert_tokens_act(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok, int W,
                                            int F, int E, int top, float limit, int act, int dtype, void* stream) {
-  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2, QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: unknown activation %d", act);
+  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2 || act == QSPEC_EXPERT_ACT_SILU, QSPEC_ERR_INVALID_ARG,
+                "moe_expert_tokens: unknown activation %d", act);
   QSPEC_REQUIRE(h && idx && out && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && W > 0 && F >= 0 && E >= 0 && top >= 1 && top <= 65535, QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: bad sizes");
   SEQ_DTYPE_OK(dtype);

@@ -95,16 +95,18 @@ add_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_prep_kernel(const T* __restrict__ d, int ld, int q_rank, int kv_rank, int rot_dim, const float* __restrict__ qn_w,
-                   const float* __restrict__ kvn_w, const float* __restrict__ inv_freq, int rot_dims, T* __restrict__ cq,
+                   const float* __restrict__ kvn_w, const float* __restrict__ inv_freq, int rot_dims, int pairing, T* __restrict__ cq,
                    T* __restrict__ cache, int cap, const int* __restrict__ meta, int ntok, float eps) {
   pdl_enter();
   __shared__ float red[8];
   const int i = blockIdx.x, tid = threadIdx.x;
   const T* row = d + (size_t)i * ld;
   float ss = 0.f;
-  for (int c = tid; c < q_rank; c += 256) { const float v = to_f(row[c]); ss += v * v; }
-  const float rq = 1.0f / sqrtf(block_sum_256(ss, red) / (float)q_rank + eps);
-  for (int c = tid; c < q_rank; c += 256) cq[(size_t)i * q_rank + c] = from_f<T>(to_f(row[c]) * rq * qn_w[c]);
+  if (q_rank > 0) {
+    for (int c = tid; c < q_rank; c += 256) { const float v = to_f(row[c]); ss += v * v; }
+    const float rq = 1.0f / sqrtf(block_sum_256(ss, red) / (float)q_rank + eps);
+    for (int c = tid; c < q_rank; c += 256) cq[(size_t)i * q_rank + c] = from_f<T>(to_f(row[c]) * rq * qn_w[c]);
+  }
   if (!cache) return;
   const int slot = meta[i], pos = meta[ntok + i];
   T* crow = cache + ((size_t)slot * cap + (pos % cap)) * (kv_rank + rot_dim);
@@ -118,9 +120,10 @@ latent_prep_kernel(const T* __restrict__ d, int ld, int q_rank, int kv_rank, int
   for (int c = tid; c < half; c += 256) {
     float sn, cs;
     sincosf((float)pos * inv_freq[c], &sn, &cs);
-    const float u = to_f(kr[c]), v = to_f(kr[c + half]);
-    crow[kv_rank + c] = from_f<T>(u * cs - v * sn);
-    crow[kv_rank + c + half] = from_f<T>(v * cs + u * sn);
+    const int iu = pairing == QSPEC_ROTARY_INTERLEAVED ? 2 * c : c, iv = pairing == QSPEC_ROTARY_INTERLEAVED ? 2 * c + 1 : c + half;
+    const float u = to_f(kr[iu]), v = to_f(kr[iv]);
+    crow[kv_rank + iu] = from_f<T>(u * cs - v * sn);
+    crow[kv_rank + iv] = from_f<T>(v * cs + u * sn);
   }
   for (int c = rot_dims + tid; c < rot_dim; c += 256) crow[kv_rank + c] = kr[c];
 }
@@ -130,7 +133,7 @@ latent_prep_kernel(const T* __restrict__ d, int ld, int q_rank, int kv_rank, int
 template <typename T>
 __global__ void __launch_bounds__(128)
 rotary_kernel(const T* __restrict__ src, long long src_ts, int src_hs, int off, float* __restrict__ dst, long long dst_ts, int dst_hs,
-              int H, int n, int rot_dims, const float* __restrict__ inv_freq, const int* __restrict__ meta, int ntok) {
+              int H, int n, int rot_dims, int pairing, const float* __restrict__ inv_freq, const int* __restrict__ meta, int ntok) {
   pdl_enter();
   const int i = blockIdx.x;
   const int pos = meta[ntok + i];
@@ -142,9 +145,10 @@ rotary_kernel(const T* __restrict__ src, long long src_ts, int src_hs, int off, 
     if (c < half) {
       float sn, cs;
       sincosf((float)pos * inv_freq[c], &sn, &cs);
-      const float u = to_f(s[c]), v = to_f(s[c + half]);
-      o[c] = u * cs - v * sn;
-      o[c + half] = v * cs + u * sn;
+      const int iu = pairing == QSPEC_ROTARY_INTERLEAVED ? 2 * c : c, iv = pairing == QSPEC_ROTARY_INTERLEAVED ? 2 * c + 1 : c + half;
+      const float u = to_f(s[iu]), v = to_f(s[iv]);
+      o[iu] = u * cs - v * sn;
+      o[iv] = v * cs + u * sn;
     } else {
       o[rot_dims + c - half] = to_f(s[rot_dims + c - half]);
     }
@@ -190,8 +194,8 @@ __global__ void __launch_bounds__(128)
 window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_hs, int DA, const float* __restrict__ qb,
                    long long qb_ts, long long qb_hs, int DB, const T* __restrict__ kc, long long k_ss, int k_rs, int k_hs,
                    const T* __restrict__ vc, long long v_ss, int v_rs, int v_hs, int DV, const float* __restrict__ sink,
-                   const T* __restrict__ gate, int gate_ld, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H,
-                   int G, int window, int cap, float scale) {
+                   const T* __restrict__ gate, int gate_ld, int gate_per_head, T* __restrict__ out, const int* __restrict__ meta,
+                   int ntok, int H, int G, int window, int cap, float scale) {
   pdl_enter();
   extern __shared__ float sm_wa[];            // q [DK] | acc [4][DV]
   __shared__ float s_m[4], s_l[4];
@@ -290,7 +294,7 @@ window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_h
 #pragma unroll
     for (int w = 0; w < 4; ++w) o += sacc[w * DV + c] * f[w];
     o *= inv;
-    if (gate) o *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)i * gate_ld + (size_t)h * DV + c])));
+    if (gate) o *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)i * gate_ld + (gate_per_head ? (size_t)h : (size_t)h * DV + c)])));
     out[((size_t)i * H + h) * DV + c] = from_f<T>(o);
   }
 }
@@ -315,6 +319,101 @@ hgrn2_gates_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_
   }
 }
 
+
+// ---- scalar-decay linear attention: q = silu(zq), k = silu(zk), float32, once per (token, row); gates [ntok][2][H * D] ----
+template <typename T>
+__global__ void __launch_bounds__(256)
+lightning_gates_kernel(const T* __restrict__ p, int ld, float* __restrict__ gates, int HD, long long n) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const long long t = k / HD;
+    const int c = (int)(k - t * HD);
+    const T* row = p + (size_t)t * ld;
+    const float zq = to_f(row[c]), zk = to_f(row[HD + c]);
+    float* g = gates + (size_t)t * 2 * HD + c;
+    g[0] = zq / (1.0f + expf(-zq));
+    g[HD] = zk / (1.0f + expf(-zk));
+  }
+}
+
+// Unit-RMS norm over a whole row of float32 values with a weight and a sigmoid gate: out = src / rms(src) * w * sigmoid(gate).
+// One CTA per row (all heads of a token are normed together).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_row_norm_kernel(const float* __restrict__ src, const float* __restrict__ w, const T* __restrict__ gate, int gate_ld,
+                      T* __restrict__ out, int N, float eps) {
+  pdl_enter();
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const float* s = src + (size_t)i * N;
+  float ss = 0.f;
+  for (int c = tid; c < N; c += 256) ss += s[c] * s[c];
+  const float rr = 1.0f / sqrtf(block_sum_256(ss, red) / (float)N + eps);
+  for (int c = tid; c < N; c += 256) {
+    const float z = to_f(gate[(size_t)i * gate_ld + c]);
+    out[(size_t)i * N + c] = from_f<T>(s[c] * rr * w[c] * (1.0f / (1.0f + expf(-z))));
+  }
+}
+
+// ---- residual sum with a multiplier, and the norm of the next sublayer's input ---------------------------------------
+// r = x_in + mult * (sum of weighted parts of y + weighted y2); out = r / sqrt(mean(r^2) + eps) * (w_offset + w). One CTA per
+// token; the row lives in shared memory between the passes.
+template <typename T, typename YT>
+__global__ void __launch_bounds__(256)
+residual_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const YT* __restrict__ y, int y_parts,
+                     long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w, const YT* __restrict__ y2,
+                     const float* __restrict__ y2_w, int y2_w_stride, float mult, const float* __restrict__ w, float w_offset,
+                     T* __restrict__ out, int W, float eps) {
+  pdl_enter();
+  extern __shared__ float sm_rn[];            // row [W]
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const YT* yr = y ? y + (size_t)i * y_tok_stride : nullptr;
+  const YT* y2r = y2 ? y2 + (size_t)i * W : nullptr;
+  const float w2 = (y2 && y2_w) ? y2_w[(size_t)i * y2_w_stride] : 1.0f;
+  float q = 0.f;
+  for (int c = tid; c < W; c += 256) {
+    float v = 0.f;
+    if (yr) {
+      if (y_parts == 1 && !y_w) v = to_f(yr[c]);
+      else
+        for (int p = 0; p < y_parts; ++p) v += (y_w ? y_w[(size_t)i * y_parts + p] : 1.0f) * to_f(yr[(size_t)p * y_part_stride + c]);
+    }
+    if (y2r) v += w2 * to_f(y2r[c]);
+    const float r = x_in[(size_t)i * W + c] + mult * v;
+    if (x_out) x_out[(size_t)i * W + c] = r;
+    sm_rn[c] = r;
+    q += r * r;
+  }
+  if (!out) return;
+  const float rr = 1.0f / sqrtf(block_sum_256(q, red) / (float)W + eps);
+  for (int c = tid; c < W; c += 256) out[(size_t)i * W + c] = from_f<T>(sm_rn[c] * rr * (w_offset + w[c]));
+}
+
+// ---- element-wise activations -------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) act_kernel(T* __restrict__ a, long long n, int act) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const float z = to_f(a[k]);
+    float v;
+    if (act == QSPEC_ACT_GELU_ERF) v = 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    else { v = fmaxf(z, 0.f); v *= v; }
+    a[k] = from_f<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int F, long long n) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const long long t = k / F;
+    const int f = (int)(k - t * F);
+    const float g = to_f(gu[(size_t)t * ld + f]), u = to_f(gu[(size_t)t * ld + F + f]);
+    out[k] = from_f<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
 // ---- HGRN2: gated linear recurrence ---------------------------------------------------------------------------------
 // Per head S <- diag(f) S + (1 - f) v^T, o = S^T q with f = lower + (1 - lower) sigmoid(zf + b) and q = silu(zq).
 // One CTA per (segment, head, slice of 16 value columns) walks the segment's tokens in order, 16 (or 8) at a time; thread
@@ -326,7 +425,8 @@ hgrn2_gates_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_
 template <typename T, int NS, int BT>
 __global__ void __launch_bounds__(256)
 hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ gates, float* __restrict__ state, float* __restrict__ o,
-                  const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int H, int D, int DV) {
+                  const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int H, int D, int DV,
+                  const float* __restrict__ decay) {
   pdl_enter();
   // with a list of the segments' first rows the grid has one CTA per segment; without it, one per token, and the CTAs of
   // tokens that do not open a segment leave at once (a long prompt then pays for thousands of empty CTAs)
@@ -345,6 +445,7 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ gat
 #pragma unroll
   for (int k = 0; k < NS; ++k) S[k] = (mt.pos > 0 && live && d0 + k < D) ? st[(size_t)(d0 + k) * DV + col] : 0.f;
   const int HD = H * D;
+  const float dec = decay ? decay[h] : 1.f;
   float rq[R], rf[R], rg[R], zv = 0.f;
   auto fetch = [&](int tb) {                               // gates and values of the block's tokens into registers
 #pragma unroll
@@ -352,13 +453,19 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ gat
       const int e = tid + 256 * r, tt = e / DP, d = e % DP, t = tb + tt;
       rq[r] = 0.f; rf[r] = 1.f; rg[r] = 0.f;
       if (t < mt.seg_end && d < D) {
-        const float* g = gates + (size_t)t * 3 * HD + h * D + d;
-        rq[r] = g[0]; rf[r] = g[HD]; rg[r] = g[2 * HD];
+        if (decay) {                                          // one decay per head: gates hold [q | k] only
+          const float* g = gates + (size_t)t * 2 * HD + h * D + d;
+          rq[r] = g[0]; rf[r] = dec; rg[r] = g[HD];
+        } else {
+          const float* g = gates + (size_t)t * 3 * HD + h * D + d;
+          rq[r] = g[0]; rf[r] = g[HD]; rg[r] = g[2 * HD];
+        }
       }
     }
     if (tid < BT * 16) {
       const int t = tb + grp;
       zv = (t < mt.seg_end && live) ? to_f(p[(size_t)t * ld + 2 * HD + h * DV + col]) : 0.f;
+      if (decay) zv = zv / (1.0f + expf(-zv));               // the scalar-decay form takes silu(v)
     }
   };
   fetch(mt.seg_begin);
@@ -493,26 +600,43 @@ extern "C" int qspec_seq_add_norm(const float* x_in, float* x_out, const void* y
 extern "C" int qspec_seq_latent_prep(const void* d, int ld, int q_rank, int kv_rank, int rot_dim, const float* qn_w, const float* kvn_w,
                                      const float* inv_freq, int rot_dims, void* cq, void* cache, int cap, const int* meta, int ntok,
                                      float eps, int dtype, void* stream) {
-  QSPEC_REQUIRE(d && qn_w && cq && meta, QSPEC_ERR_INVALID_ARG, "seq_latent_prep: null pointer");
+  QSPEC_REQUIRE(q_rank > 0, QSPEC_ERR_INVALID_ARG, "seq_latent_prep: bad sizes");
+  return qspec_seq_latent_prep_pairing(d, ld, q_rank, kv_rank, rot_dim, qn_w, kvn_w, inv_freq, rot_dims, QSPEC_ROTARY_HALVES, cq, cache, cap,
+                                       meta, ntok, eps, dtype, stream);
+}
+
+extern "C" int qspec_seq_latent_prep_pairing(const void* d, int ld, int q_rank, int kv_rank, int rot_dim, const float* qn_w,
+                                             const float* kvn_w, const float* inv_freq, int rot_dims, int pairing, void* cq, void* cache,
+                                             int cap, const int* meta, int ntok, float eps, int dtype, void* stream) {
+  QSPEC_REQUIRE(d && meta && (q_rank == 0 || (qn_w && cq)), QSPEC_ERR_INVALID_ARG, "seq_latent_prep: null pointer");
+  QSPEC_REQUIRE(pairing == QSPEC_ROTARY_HALVES || pairing == QSPEC_ROTARY_INTERLEAVED, QSPEC_ERR_INVALID_ARG, "seq_latent_prep: unknown pairing %d", pairing);
   QSPEC_REQUIRE(!cache || (kvn_w && (inv_freq || rot_dims == 0)), QSPEC_ERR_INVALID_ARG,
                 "seq_latent_prep: a cache needs the key/value norm weight and the frequencies");
-  QSPEC_REQUIRE(ntok >= 0 && q_rank > 0 && kv_rank >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 &&
+  QSPEC_REQUIRE(ntok >= 0 && q_rank >= 0 && kv_rank >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 &&
                     cap > 0 && ld >= q_rank + (cache ? kv_rank + rot_dim : 0),
                 QSPEC_ERR_INVALID_ARG, "seq_latent_prep: bad sizes");
   MIX_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   if (dtype == QSPEC_DTYPE_F32)
     launch_pdl(latent_prep_kernel<float>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const float*)d, ld, q_rank, kv_rank, rot_dim,
-               qn_w, kvn_w, inv_freq, rot_dims, (float*)cq, (float*)cache, cap, meta, ntok, eps);
+               qn_w, kvn_w, inv_freq, rot_dims, pairing, (float*)cq, (float*)cache, cap, meta, ntok, eps);
   else
     launch_pdl(latent_prep_kernel<bf16_t>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const bf16_t*)d, ld, q_rank, kv_rank, rot_dim,
-               qn_w, kvn_w, inv_freq, rot_dims, (bf16_t*)cq, (bf16_t*)cache, cap, meta, ntok, eps);
+               qn_w, kvn_w, inv_freq, rot_dims, pairing, (bf16_t*)cq, (bf16_t*)cache, cap, meta, ntok, eps);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
 
 extern "C" int qspec_seq_rotary(const void* src, long long src_ts, int src_hs, int off, float* dst, long long dst_ts, int dst_hs, int H,
                                 int n, int rot_dims, const float* inv_freq, const int* meta, int ntok, int dtype, void* stream) {
+  return qspec_seq_rotary_pairing(src, src_ts, src_hs, off, dst, dst_ts, dst_hs, H, n, rot_dims, QSPEC_ROTARY_HALVES, inv_freq, meta, ntok,
+                                  dtype, stream);
+}
+
+extern "C" int qspec_seq_rotary_pairing(const void* src, long long src_ts, int src_hs, int off, float* dst, long long dst_ts, int dst_hs,
+                                        int H, int n, int rot_dims, int pairing, const float* inv_freq, const int* meta, int ntok,
+                                        int dtype, void* stream) {
+  QSPEC_REQUIRE(pairing == QSPEC_ROTARY_HALVES || pairing == QSPEC_ROTARY_INTERLEAVED, QSPEC_ERR_INVALID_ARG, "seq_rotary: unknown pairing %d", pairing);
   QSPEC_REQUIRE(src && dst && meta && (rot_dims == 0 || inv_freq), QSPEC_ERR_INVALID_ARG, "seq_rotary: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && H > 0 && n >= 0 && rot_dims >= 0 && rot_dims <= n && rot_dims % 2 == 0, QSPEC_ERR_INVALID_ARG,
                 "seq_rotary: bad sizes");
@@ -520,10 +644,10 @@ extern "C" int qspec_seq_rotary(const void* src, long long src_ts, int src_hs, i
   if (ntok == 0 || n == 0) return QSPEC_OK;
   if (dtype == QSPEC_DTYPE_F32)
     launch_pdl(rotary_kernel<float>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const float*)src, src_ts, src_hs, off, dst, dst_ts,
-               dst_hs, H, n, rot_dims, inv_freq, meta, ntok);
+               dst_hs, H, n, rot_dims, pairing, inv_freq, meta, ntok);
   else
     launch_pdl(rotary_kernel<bf16_t>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const bf16_t*)src, src_ts, src_hs, off, dst, dst_ts,
-               dst_hs, H, n, rot_dims, inv_freq, meta, ntok);
+               dst_hs, H, n, rot_dims, pairing, inv_freq, meta, ntok);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
@@ -555,7 +679,7 @@ static int launch_window_attn(const qspec_window_attn_args* a, cudaStream_t st) 
   }
   launch_pdl(window_attn_kernel<T, NACC, VEC>, dim3(a->ntok, a->H), dim3(128), smem, st, a->qa, a->qa_tok_stride, a->qa_head_stride, a->DA,
              a->qb, a->qb_tok_stride, a->qb_head_stride, a->DB, (const T*)a->k, a->k_slot_stride, a->k_row_stride, a->k_head_stride,
-             (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->DV, a->sink, (const T*)a->gate, a->gate_ld, (T*)a->out,
+             (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->DV, a->sink, (const T*)a->gate, a->gate_ld, a->gate_per_head, (T*)a->out,
              a->meta, a->ntok, a->H, a->G, a->window, a->cap, a->scale);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
@@ -591,14 +715,15 @@ extern "C" int qspec_seq_window_attention(const qspec_window_attn_args* a, int d
 
 template <typename T>
 static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, float* gates, const int* meta,
-                        const int* seg_starts, int nseg, int ntok, int H, int D, int DV, cudaStream_t st) {
+                        const int* seg_starts, int nseg, int ntok, int H, int D, int DV, cudaStream_t st, const float* decay = nullptr) {
   const long long n = (long long)ntok * H * D;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  launch_pdl(hgrn2_gates_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)p, ld, f_b, lower, gates, H * D, n);
+  if (decay) launch_pdl(lightning_gates_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)p, ld, gates, H * D, n);
+  else launch_pdl(hgrn2_gates_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)p, ld, f_b, lower, gates, H * D, n);
   QSPEC_CHECK_LAUNCH(1);
   const dim3 grid(seg_starts ? nseg : ntok, H, (DV + 15) / 16);
-#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, (const float*)gates, state, o, meta, seg_starts, ntok, H, D, DV
+#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, (const float*)gates, state, o, meta, seg_starts, ntok, H, D, DV, decay
   // blocks of 16 tokens for prompt portions (fewer barriers and copies per token); 8 for decoding steps, where the state's
   // way in and out of the registers is the work and the smaller shared-memory footprint keeps more CTAs on an SM
   const bool longs = seg_starts && ntok >= 16 * nseg;
@@ -649,6 +774,94 @@ extern "C" int qspec_seq_side_gate(void* g, const void* table, const int* ids, i
   else
     launch_pdl(side_gate_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (bf16_t*)g, (const bf16_t*)table, ids,
                col0, sd, table_ld, V, n);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T, typename YT>
+static int launch_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
+                                const float* y_w, const void* y2, const float* y2_w, int y2_w_stride, float mult, const float* w,
+                                float w_offset, void* out, int ntok, int W, float eps, cudaStream_t st) {
+  const size_t smem = (size_t)W * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(residual_norm_kernel<T, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  launch_pdl(residual_norm_kernel<T, YT>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const YT*)y, y_parts, y_part_stride, y_tok_stride,
+             y_w, (const YT*)y2, y2_w, y2_w_stride, mult, w, w_offset, (T*)out, W, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                       long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
+                                       float mult, const float* w, float w_offset, void* out, int ntok, int W, float eps, int y_dtype,
+                                       int dtype, void* stream) {
+  QSPEC_REQUIRE(x_in && (x_out || out) && (!out || w), QSPEC_ERR_INVALID_ARG, "seq_residual_norm: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && W <= 49152 && y_parts >= 1 && y2_w_stride >= 0, QSPEC_ERR_INVALID_ARG,
+                "seq_residual_norm: bad sizes (width <= 49152)");
+  MIX_DTYPE_OK(dtype);
+  QSPEC_REQUIRE(y_dtype == dtype || y_dtype == QSPEC_DTYPE_F32, QSPEC_ERR_UNSUPPORTED, "seq_residual_norm: y is of the activation type or float32");
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+#define RN_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset, out, ntok, W, eps, st
+  if (dtype == QSPEC_DTYPE_F32) return launch_residual_norm<float, float>(RN_ARGS);
+  if (y_dtype == QSPEC_DTYPE_F32) return launch_residual_norm<bf16_t, float>(RN_ARGS);
+  return launch_residual_norm<bf16_t, bf16_t>(RN_ARGS);
+#undef RN_ARGS
+}
+
+extern "C" int qspec_seq_act(void* a, long long n, int act, int dtype, void* stream) {
+  QSPEC_REQUIRE(a && n >= 0, QSPEC_ERR_INVALID_ARG, "seq_act: bad arguments");
+  QSPEC_REQUIRE(act == QSPEC_ACT_RELU2 || act == QSPEC_ACT_GELU_ERF, QSPEC_ERR_INVALID_ARG, "seq_act: unknown activation %d", act);
+  MIX_DTYPE_OK(dtype);
+  if (n == 0) return QSPEC_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == QSPEC_DTYPE_F32) launch_pdl(act_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (float*)a, n, act);
+  else launch_pdl(act_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (bf16_t*)a, n, act);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_silu_mul(const void* gu, int ld, void* out, int ntok, int F, int dtype, void* stream) {
+  QSPEC_REQUIRE(gu && out && ntok >= 0 && F > 0 && ld >= 2 * F, QSPEC_ERR_INVALID_ARG, "seq_silu_mul: bad arguments");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const long long n = (long long)ntok * F;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(silu_mul_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const float*)gu, ld, (float*)out, F, n);
+  else
+    launch_pdl(silu_mul_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const bf16_t*)gu, ld, (bf16_t*)out, F, n);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_lightning(const void* p, int ld, const float* decay, const float* norm_w, float* state, float* scratch, void* out,
+                                   const int* meta, const int* seg_starts, int nseg, int ntok, int H, int D, int DV, float eps, int dtype,
+                                   void* stream) {
+  QSPEC_REQUIRE(!seg_starts || (nseg >= 1 && nseg <= ntok) || ntok == 0, QSPEC_ERR_INVALID_ARG, "seq_lightning: %d segments for %d tokens", nseg, ntok);
+  QSPEC_REQUIRE(p && decay && norm_w && state && scratch && out && meta, QSPEC_ERR_INVALID_ARG, "seq_lightning: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && H <= 65535 && D > 0 && D <= 256 && DV > 0 && DV <= 65535 * 16 && ld >= 2 * H * D + 2 * H * DV,
+                QSPEC_ERR_UNSUPPORTED, "seq_lightning: %d heads, key size %d (<= 256), value size %d", H, D, DV);
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* gates = scratch + (size_t)ntok * H * DV;          // scratch: un-normalised outputs, then silu(q) and silu(k)
+  int s = dtype == QSPEC_DTYPE_F32
+              ? launch_hgrn2<float>(p, ld, nullptr, nullptr, state, scratch, gates, meta, seg_starts, nseg, ntok, H, D, DV, st, decay)
+              : launch_hgrn2<bf16_t>(p, ld, nullptr, nullptr, state, scratch, gates, meta, seg_starts, nseg, ntok, H, D, DV, st, decay);
+  if (s) return s;
+  const int N = H * DV, goff = 2 * H * D + H * DV;         // the output gate's logits follow q, k and v in the row
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(gated_row_norm_kernel<float>, dim3(ntok), dim3(256), 0, st, (const float*)scratch, norm_w, (const float*)p + goff, ld,
+               (float*)out, N, eps);
+  else
+    launch_pdl(gated_row_norm_kernel<bf16_t>, dim3(ntok), dim3(256), 0, st, (const float*)scratch, norm_w, (const bf16_t*)p + goff, ld,
+               (bf16_t*)out, N, eps);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }

@@ -693,7 +693,7 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 template <int MODE>
 __global__ void __launch_bounds__(256)
 grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, GroupPlan p, int K, int N, int top,
-                       float limit) {
+                       float limit, int act) {
   pdl_enter();
   extern __shared__ __align__(16) unsigned char tc_smem_raw[];
   __shared__ int s_row[GG_BM];
@@ -807,9 +807,15 @@ grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, b
       for (int x = 0; x < 16; ++x) {
         if (DUAL) {
           // projections leave the matrix unit in bfloat16, like the dense layers' products
-          const float gv = fminf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), limit);
-          const float uv = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(b[x]))), -limit), limit);
-          v[x] = gv * (1.0f / (1.0f + expf(-1.702f * gv))) * (uv + 1.0f);
+          if (act == QSPEC_EXPERT_ACT_SILU) {
+            const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x])));
+            const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(b[x])));
+            v[x] = gv / (1.0f + expf(-gv)) * uv;
+          } else {
+            const float gv = fminf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), limit);
+            const float uv = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(b[x]))), -limit), limit);
+            v[x] = gv * (1.0f / (1.0f + expf(-1.702f * gv))) * (uv + 1.0f);
+          }
         } else if (MODE == 2) {
           const float u = fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), 0.f);
           v[x] = u * u;
@@ -888,7 +894,8 @@ extern "C" size_t qspec_moe_grouped_workspace_bytes(int ntok, int top, int E, in
 extern "C" int qspec_moe_expert_grouped_act(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
                                             int W, int F, int E, int top, float limit, int act, void* workspace,
                                             size_t workspace_bytes, void* stream) {
-  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2, QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: unknown activation %d", act);
+  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2 || act == QSPEC_EXPERT_ACT_SILU, QSPEC_ERR_INVALID_ARG,
+                "moe_expert_grouped: unknown activation %d", act);
   QSPEC_REQUIRE(h && idx && out && workspace && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && top >= 1 && E >= 0 && E <= 8192, QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: bad sizes");
   QSPEC_REQUIRE(qspec_moe_expert_grouped_supported(W, F), QSPEC_ERR_UNSUPPORTED,
@@ -927,13 +934,13 @@ extern "C" int qspec_moe_expert_grouped_act(const void* h, const void* gate_up, 
   if (!warp_level) {
     if (act == QSPEC_EXPERT_ACT_RELU2)
       launch_pdl(grouped_gemm_tc_kernel<2>, dim3(max_tiles, (F + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
-                 p, W, F, top, limit);
+                 p, W, F, top, limit, act);
     else
       launch_pdl(grouped_gemm_tc_kernel<1>, dim3(max_tiles, (F + 63) / 64), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
-                 p, W, F, top, limit);
+                 p, W, F, top, limit, act);
     QSPEC_CHECK_LAUNCH(1);
     launch_pdl(grouped_gemm_tc_kernel<0>, dim3(max_tiles, (W + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)Y, (const bf16*)down,
-               (bf16*)out, p, F, W, top, limit);
+               (bf16*)out, p, F, W, top, limit, act);
     QSPEC_CHECK_LAUNCH(1);
     return QSPEC_OK;
   }
@@ -971,7 +978,7 @@ struct WinMma {
   const bf16* kA; long long kA_ss; int kA_rs, kA_hs;
   const bf16* kB; long long kB_ss; int kB_rs;
   const bf16* v; long long v_ss; int v_rs, v_hs;
-  const float* sink; const bf16* gate; int gate_ld;
+  const float* sink; const bf16* gate; int gate_ld, gate_per_head;
   bf16* out; int out_hs; const int* meta; int ntok, H, G, window, cap; float scale; int token_rows;
 };
 
@@ -1192,7 +1199,7 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
       acc += sO[(w * 16 + row) * DV + d] * f;
     }
     float r = acc / L;
-    if (a.gate) r *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)tok * a.gate_ld + (size_t)head * a.out_hs + (size_t)blockIdx.z * DV + d])));
+    if (a.gate) r *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)tok * a.gate_ld + (a.gate_per_head ? (size_t)head : (size_t)head * a.out_hs + (size_t)blockIdx.z * DV + d)])));
     a.out[((size_t)tok * a.H + head) * a.out_hs + (size_t)blockIdx.z * DV + d] = __float2bfloat16_rn(r);
   }
 }
@@ -1374,7 +1381,9 @@ __global__ void __launch_bounds__(256) latent_absorbed_mma_kernel(const WinMma a
             acc[t][e] += fr * __uint_as_float(ld_dsmem_u32(
                              mapa_shared(part + 4u * (uint32_t)(32 + row * DA + 64 * warp + 8 * (2 * tig + e) + t), (uint32_t)r)));
       }
-      const float inv = 1.0f / L;
+      float inv = 1.0f / L;
+      // one output gate per head (a scalar commutes with the value up-projection that follows)
+      if (a.gate) inv *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)i * a.gate_ld + head])));
       bf16* orow = a.out + ((size_t)i * a.H + head) * a.out_hs + 64 * warp;
 #pragma unroll
       for (int t = 0; t < 8; ++t)
@@ -1462,13 +1471,13 @@ int window_attention_mma(const qspec_window_attn_args* p, const void* kB, long l
   a.kA = (const bf16*)p->k; a.kA_ss = p->k_slot_stride; a.kA_rs = p->k_row_stride; a.kA_hs = p->k_head_stride;
   a.kB = (const bf16*)kB; a.kB_ss = kB_ss; a.kB_rs = kB_rs;
   a.v = (const bf16*)p->v; a.v_ss = p->v_slot_stride; a.v_rs = p->v_row_stride; a.v_hs = p->v_head_stride;
-  a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld;
+  a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld; a.gate_per_head = p->gate_per_head;
   a.out = (bf16*)p->out; a.out_hs = DV; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
   a.scale = p->scale; a.token_rows = token_rows;
   // a latent cache read in the absorbed form (keys and values are the same rows): the CTA-level kernel; QSPEC_SEQ_LATENT=sliced
   // keeps the form with one CTA per slice of 128 value columns, for comparison
   static const bool sliced = [] { const char* v = getenv("QSPEC_SEQ_LATENT"); return v && !strcmp(v, "sliced"); }();
-  if (!sliced && !token_rows && DA >= 256 && DV == DA && p->v == p->k && !p->gate) {
+  if (!sliced && !token_rows && DA >= 256 && DV == DA && p->v == p->k && (!p->gate || p->gate_per_head)) {
     if (DA == 512) return launch_latent_absorbed<512>(a, st);
     return launch_latent_absorbed<256>(a, st);
   }

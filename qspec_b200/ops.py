@@ -870,14 +870,14 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, correction: torch.Tensor,
                                          _stream()), "moe_route")
 
 
-EXPERT_ACTS = {"gated": 0, "relu2": 1}       # QSPEC_EXPERT_ACT_* of include/qspec_b200_seq.h
+EXPERT_ACTS = {"gated": 0, "relu2": 1, "silu": 2}       # QSPEC_EXPERT_ACT_* of include/qspec_b200_seq.h
 
 
 def moe_expert_tokens(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Optional[torch.Tensor], idx: torch.Tensor,
                       out: torch.Tensor, E: int, F: int, limit: float, act: str = "gated") -> None:
     """Expert outputs per (token, choice), unweighted: out [ntok, top, W]; choices >= E copy h (identity experts).
-    act "gated": gate_up [E, 2F, W], the clamped gated activation; "relu2": gate_up is the up matrix [E, F, W] alone and
-    the activation is the squared ReLU (limit unused)."""
+    act "gated": gate_up [E, 2F, W], the clamped gated activation; "silu": the same rows with silu(gate) * up (limit unused);
+    "relu2": gate_up is the up matrix [E, F, W] alone and the activation is the squared ReLU (limit unused)."""
     _chk(h, "h", _SEQ_ACT); _chk(out, "out", (h.dtype,)); _chk(idx, "idx", (torch.int32,))
     _chk(gate_up, "gate_up", (h.dtype,), allow_none=E == 0); _chk(down, "down", (h.dtype,), allow_none=E == 0)
     ntok, W = h.shape
@@ -962,31 +962,38 @@ def seq_add_norm(y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], ep
          "seq_add_norm")
 
 
-def seq_latent_prep(d: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, qn_w: torch.Tensor, kvn_w: Optional[torch.Tensor],
-                    inv_freq: Optional[torch.Tensor], rot_dims: int, cq: torch.Tensor, cache: Optional[torch.Tensor],
-                    meta: torch.Tensor, eps: float) -> None:
+ROTARY_PAIRINGS = {"halves": 0, "interleaved": 1}      # QSPEC_ROTARY_* of include/qspec_b200_seq.h
+
+
+def seq_latent_prep(d: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, qn_w: Optional[torch.Tensor], kvn_w: Optional[torch.Tensor],
+                    inv_freq: Optional[torch.Tensor], rot_dims: int, cq: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                    meta: torch.Tensor, eps: float, pairing: str = "halves") -> None:
     """Norms of the low-rank query / key-value projections and the rotary key part; with `cache` [slots, cap, kv_rank + rot_dim]
-    the step's rows are written at position % cap."""
-    _chk(d, "d", _SEQ_ACT); _chk(cq, "cq", (d.dtype,)); _chk(cache, "cache", (d.dtype,), allow_none=True)
-    _chk(qn_w, "qn_w", (_F32,)); _chk(kvn_w, "kvn_w", (_F32,), allow_none=True); _chk(inv_freq, "inv_freq", (_F32,), allow_none=True)
+    the step's rows are written at position % cap. q_rank 0: the rows hold no query latent (qn_w and cq None). pairing: which
+    entries of the rotary part turn together, (i, i + rot_dims / 2) "halves" or (2i, 2i + 1) "interleaved"."""
+    _chk(d, "d", _SEQ_ACT); _chk(cq, "cq", (d.dtype,), allow_none=q_rank == 0); _chk(cache, "cache", (d.dtype,), allow_none=True)
+    _chk(qn_w, "qn_w", (_F32,), allow_none=q_rank == 0); _chk(kvn_w, "kvn_w", (_F32,), allow_none=True)
+    _chk(inv_freq, "inv_freq", (_F32,), allow_none=True)
     ntok = d.shape[0]
-    if cq.shape != (ntok, q_rank) or (cache is not None and cache.shape[2] != kv_rank + rot_dim):
+    if (q_rank and cq.shape != (ntok, q_rank)) or (cache is not None and cache.shape[2] != kv_rank + rot_dim):
         raise ValueError("seq_latent_prep: shapes do not match")
     cap = cache.shape[1] if cache is not None else 1
-    _seq(_lib.load_seq().qspec_seq_latent_prep(_ptr(d), d.shape[1], q_rank, kv_rank, rot_dim, _ptr(qn_w), _ptr(kvn_w), _ptr(inv_freq),
-                                               rot_dims, _ptr(cq), _ptr(cache), cap, _ptr(meta), ntok, float(eps), _sdt(d), _stream()),
-         "seq_latent_prep")
+    _seq(_lib.load_seq().qspec_seq_latent_prep_pairing(_ptr(d), d.shape[1], q_rank, kv_rank, rot_dim, _ptr(qn_w), _ptr(kvn_w),
+                                                       _ptr(inv_freq), rot_dims, ROTARY_PAIRINGS[pairing], _ptr(cq), _ptr(cache), cap,
+                                                       _ptr(meta), ntok, float(eps), _sdt(d), _stream()), "seq_latent_prep")
 
 
-def seq_rotary(src: torch.Tensor, off: int, dst: torch.Tensor, rot_dims: int, inv_freq: torch.Tensor, meta: torch.Tensor) -> None:
+def seq_rotary(src: torch.Tensor, off: int, dst: torch.Tensor, rot_dims: int, inv_freq: torch.Tensor, meta: torch.Tensor,
+               pairing: str = "halves") -> None:
     """dst [ntok, H, n] float32 (a view with a unit last stride will do) = rotary positions on src[t, h, off : off + n]
-    (src [ntok, H, head size])."""
+    (src [ntok, H, head size]); pairing as for `seq_latent_prep`."""
     _chk(src, "src", _SEQ_ACT); _chk(inv_freq, "inv_freq", (_F32,))
     ntok, H, n = dst.shape
     if dst.dtype != _F32 or not dst.is_cuda or dst.stride(2) != 1 or src.shape[:2] != (ntok, H) or off + n > src.shape[2]:
         raise ValueError("seq_rotary: shapes do not match")
-    _seq(_lib.load_seq().qspec_seq_rotary(_ptr(src), H * src.shape[2], src.shape[2], off, dst.data_ptr(), dst.stride(0), dst.stride(1), H,
-                                          n, rot_dims, _ptr(inv_freq), _ptr(meta), ntok, _sdt(src), _stream()), "seq_rotary")
+    _seq(_lib.load_seq().qspec_seq_rotary_pairing(_ptr(src), H * src.shape[2], src.shape[2], off, dst.data_ptr(), dst.stride(0),
+                                                  dst.stride(1), H, n, rot_dims, ROTARY_PAIRINGS[pairing], _ptr(inv_freq), _ptr(meta),
+                                                  ntok, _sdt(src), _stream()), "seq_rotary")
 
 
 def seq_qkv_prep(p: torch.Tensor, HD: int, GD: int, GDV: int, qn_w: torch.Tensor, kn_w: torch.Tensor, qout: torch.Tensor,
@@ -1005,11 +1012,12 @@ def seq_qkv_prep(p: torch.Tensor, HD: int, GD: int, GDV: int, qn_w: torch.Tensor
 
 def seq_window_attention(qa: torch.Tensor, qb: Optional[torch.Tensor], cache_k: torch.Tensor, cache_v: torch.Tensor, out: torch.Tensor,
                          meta: torch.Tensor, window: int, scale: float, sink: Optional[torch.Tensor] = None,
-                         gate: Optional[torch.Tensor] = None) -> None:
+                         gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
     """Sliding-window softmax attention with a per-head sink over ring caches.
     qa [ntok, H, DA] and qb [ntok, H, DB] (float32, any strides with a unit last stride): the two parts of the query;
     cache_k [slots, cap, G, DA + DB], cache_v [slots, cap, G, DV] (views with a unit last stride: a latent cache passes two
-    views of one buffer); out [ntok, H, DV]; gate [ntok, >= H * DV] (sigmoid applied) or None."""
+    views of one buffer); out [ntok, H, DV]; gate [ntok, >= H * DV] (sigmoid applied) or None; gate_per_head: gate is [ntok, >= H],
+    one number per head. sink None: an ordinary softmax."""
     import ctypes
     if qa.dtype != _F32 or (qb is not None and qb.dtype != _F32):
         raise ValueError("seq_window_attention: queries are float32")
@@ -1031,7 +1039,7 @@ def seq_window_attention(qa: torch.Tensor, qb: Optional[torch.Tensor], cache_k: 
                             cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
                             cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), DV,
                             _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
-                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale))
+                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale), int(gate_per_head))
     _seq(_lib.load_seq().qspec_seq_window_attention(ctypes.byref(a), _sdt(out), _stream()), "seq_window_attention")
 
 
@@ -1043,7 +1051,8 @@ def seq_window_attention_mma_supported(out_dtype, DA: int, DB: int, DV: int, H: 
 
 def seq_window_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: Optional[torch.Tensor], cache_v: torch.Tensor,
                              out: torch.Tensor, meta: torch.Tensor, window: int, scale: float, token_rows: bool,
-                             sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                             sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                             gate_per_head: bool = False) -> None:
     """`seq_window_attention` on the tensor cores (bfloat16). q [ntok, H, DK] float32; cache_k [slots, cap, G, DA] holds the
     per-head part of the keys and k_shared [slots, cap, DB] (or None) the part all heads share, DK = DA + DB; cache_v
     [slots, cap, G, DV] (views: a slot stride of 0 serves one buffer to every slot). token_rows: False = the rows of the
@@ -1067,7 +1076,7 @@ def seq_window_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: O
                             cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
                             cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), DV,
                             _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
-                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale))
+                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale), int(gate_per_head))
     _seq(_lib.load_seq().qspec_seq_window_attention_mma(ctypes.byref(a), k_shared.data_ptr() if k_shared is not None else None,
                                                         k_shared.stride(0) if k_shared is not None else 0,
                                                         k_shared.stride(1) if k_shared is not None else 0, DB, int(token_rows), _stream()),
@@ -1098,3 +1107,105 @@ def seq_side_gate(g: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0:
     ntok, sd = g.shape
     _seq(_lib.load_seq().qspec_seq_side_gate(_ptr(g), _ptr(table), _ptr(ids), col0, sd, table.shape[1], table.shape[0], ntok, _sdt(g),
                                              _stream()), "seq_side_gate")
+
+
+def seq_residual_norm(x_in: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, y: Optional[torch.Tensor] = None,
+                      y_w: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None, y2_w: Optional[torch.Tensor] = None,
+                      mult: float = 1.0, w_offset: float = 1.0, x_out: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None) -> None:
+    """r = x_in + mult * (sum of y's parts, each times y_w [ntok, parts] if given, + y2_w * y2); out = r / rms(r) * (w_offset + w).
+    y [ntok, W] or [ntok, parts, W]; y2 [ntok, W] with one weight per token (y2_w: a float32 vector view, any stride). r goes to
+    x_out (float32; may be x_in), the norm to out (activation type). w_offset 1: the weight is stored around zero; 0: plain."""
+    _chk(x_in, "x_in", (_F32,)); _chk(w, "w", (_F32,), allow_none=out is None); _chk(x_out, "x_out", (_F32,), allow_none=True)
+    _chk(out, "out", _SEQ_ACT, allow_none=True); _chk(y, "y", _SEQ_ACT, allow_none=True); _chk(y_w, "y_w", (_F32,), allow_none=True)
+    ntok, W = x_in.shape
+    parts, pstride, tstride = 1, 0, W
+    if y is not None:
+        if y.dim() == 3:
+            parts, pstride, tstride = y.shape[1], W, y.shape[1] * W
+        if y.shape[0] != ntok or y.shape[-1] != W or (y_w is not None and y_w.shape != (ntok, parts)):
+            raise ValueError("seq_residual_norm: y / y_w shapes do not match x")
+    w2_stride = 0
+    if y2 is not None:
+        _chk(y2, "y2", (y.dtype,) if y is not None else _SEQ_ACT)
+        if y2.shape != (ntok, W):
+            raise ValueError("seq_residual_norm: y2 must be [ntok, W]")
+        if y2_w is not None:
+            if y2_w.dtype != _F32 or not y2_w.is_cuda or y2_w.dim() != 1 or y2_w.shape[0] != ntok:
+                raise ValueError("seq_residual_norm: y2_w must be a float32 vector of ntok entries")
+            w2_stride = y2_w.stride(0)
+    for t in (x_out, out):
+        if t is not None and t.shape != (ntok, W):
+            raise ValueError("seq_residual_norm: shapes do not match")
+    if w is not None and w.numel() != W:
+        raise ValueError("seq_residual_norm: the norm weight has W entries")
+    src = y if y is not None else y2
+    act = _sdt(out) if out is not None else (_sdt(src) if src is not None and src.dtype != _F32 else _lib.DTYPE_F32)
+    ydt = _sdt(src) if src is not None else act
+    _seq(_lib.load_seq().qspec_seq_residual_norm(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(y2),
+                                                 y2_w.data_ptr() if y2_w is not None else None, w2_stride, float(mult), _ptr(w),
+                                                 float(w_offset), _ptr(out), ntok, W, float(eps), ydt, act, _stream()),
+         "seq_residual_norm")
+
+
+SEQ_ACTS = {"relu2": 0, "gelu_erf": 1}                 # QSPEC_ACT_* of include/qspec_b200_seq.h
+
+
+def seq_act(a: torch.Tensor, act: str) -> None:
+    """a <- act(a) in place: "relu2" (squared ReLU) or "gelu_erf" (the exact GELU)."""
+    _chk(a, "a", _SEQ_ACT)
+    _seq(_lib.load_seq().qspec_seq_act(_ptr(a), a.numel(), SEQ_ACTS[act], _sdt(a), _stream()), "seq_act")
+
+
+def seq_silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+    """out [ntok, F] = silu(gu[:, :F]) * gu[:, F:] for rows [gate | up]."""
+    _chk(gu, "gu", _SEQ_ACT); _chk(out, "out", (gu.dtype,))
+    ntok, F = out.shape
+    if gu.shape != (ntok, 2 * F):
+        raise ValueError("seq_silu_mul: gu must be [ntok, 2 F]")
+    _seq(_lib.load_seq().qspec_seq_silu_mul(_ptr(gu), 2 * F, _ptr(out), ntok, F, _sdt(gu), _stream()), "seq_silu_mul")
+
+
+def seq_lightning(p: torch.Tensor, decay: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, scratch: torch.Tensor,
+                  out: torch.Tensor, meta: torch.Tensor, H: int, D: int, DV: int, eps: float,
+                  seg_starts: Optional[torch.Tensor] = None) -> None:
+    """Linear attention with one decay per head over rows [zq | zk | zv | zg] (silu on q, k, v; state S <- decay S + k v^T, float32
+    [slots, H, D, DV]); out [ntok, H * DV] = the heads normed together, times norm_w and sigmoid(zg). scratch float32 with room for
+    ntok * H * (DV + 2 D) values. seg_starts as for `seq_hgrn2`."""
+    _chk(seg_starts, "seg_starts", (torch.int32,), allow_none=True)
+    _chk(p, "p", _SEQ_ACT); _chk(out, "out", (p.dtype,)); _chk(state, "state", (_F32,)); _chk(scratch, "scratch", (_F32,))
+    _chk(decay, "decay", (_F32,)); _chk(norm_w, "norm_w", (_F32,))
+    ntok = p.shape[0]
+    if out.shape != (ntok, H * DV) or state.shape[1:] != (H, D, DV) or scratch.numel() < ntok * H * (DV + 2 * D) or \
+            norm_w.numel() != H * DV or decay.numel() != H or p.shape[1] < 2 * H * (D + DV) or meta.shape != (5, ntok):
+        raise ValueError("seq_lightning: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_lightning(_ptr(p), p.shape[1], _ptr(decay), _ptr(norm_w), _ptr(state), _ptr(scratch), _ptr(out),
+                                             _ptr(meta), _ptr(seg_starts), 0 if seg_starts is None else seg_starts.numel(), ntok, H, D,
+                                             DV, float(eps), _sdt(p), _stream()), "seq_lightning")
+
+
+def moe_route_grouped(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Tensor], idx: torch.Tensor,
+                      weight: torch.Tensor, *, score: str = "sigmoid", groups: int = 1, keep: int = 1, group_top: int = 2,
+                      scale: float = 1.0, extra: Optional[torch.Tensor] = None) -> None:
+    """Router with expert groups: scores s = sigmoid or softmax of router_w h (float32), choice = s + correction; the experts form
+    `groups` equal groups of neighbours, a group scores the sum of its `group_top` largest choices and only the `keep` best groups
+    stay; idx int32 [ntok, top] = the largest remaining choices, weight float32 [ntok, top] = scale * s. Rows of router_w past the
+    experts ([R + n, W]) are gate rows: extra float32 [ntok, n] (a view with a unit last stride) receives their sigmoid."""
+    _chk(h, "h", _SEQ_ACT); _chk(router_w, "router_w", (_F32,)); _chk(correction, "correction", (_F32,), allow_none=True)
+    _chk(idx, "idx", (torch.int32,)); _chk(weight, "weight", (_F32,))
+    ntok, W = h.shape
+    top = idx.shape[1]
+    n_extra = 0
+    if extra is not None:
+        if extra.dtype != _F32 or not extra.is_cuda or extra.dim() != 2 or extra.shape[0] != ntok or extra.stride(1) != 1:
+            raise ValueError("moe_route_grouped: extra must be float32 [ntok, n] with a unit last stride")
+        n_extra = extra.shape[1]
+    R = router_w.shape[0] - n_extra
+    if router_w.shape[1] != W or R < 1 or (correction is not None and correction.numel() != R) or idx.shape != (ntok, top) or \
+            weight.shape != (ntok, top):
+        raise ValueError("moe_route_grouped: shapes do not match")
+    _seq(_lib.load_seq().qspec_moe_route_grouped(_ptr(h), _ptr(router_w), _ptr(correction), _ptr(idx), _ptr(weight),
+                                                 extra.data_ptr() if extra is not None else None,
+                                                 extra.stride(0) if extra is not None else 0, ntok, W, R, top,
+                                                 {"softmax": 0, "sigmoid": 1}[score], int(groups), int(keep), int(group_top),
+                                                 float(scale), n_extra, _sdt(h), _stream()), "moe_route_grouped")
