@@ -383,7 +383,7 @@ class RepepelModel(torch.nn.Module):
         gate = d[:, r + R:]                                                         # one logit per head
         cache = self.latent_cache[run]
         ops.seq_latent_prep(d, 0, r, R, None, p.dkv_norm, p.inv_freq, m.rot_dims, None, cache, tab, self.cfg.eps, pairing="interleaved")
-        if prompt_shaped and len(meta.segments) == 1 and id(m) in self._lat_tiles and ld % 8 == 0:
+        if prompt_shaped and len(meta.segments) == 1 and id(m) in self._lat_tiles:
             # expanded form on the tensor cores: per-head keys and values of the rows this sequence holds after the step
             slot, rows, cap = meta.segments[0][1], meta.max_length, cache.shape[1]
             ring = cache[slot, :rows]
@@ -409,7 +409,7 @@ class RepepelModel(torch.nn.Module):
         ops.seq_rotary(q, m.dim, qf[:, :, r:], m.rot_dims, p.inv_freq, tab, pairing="interleaved")
         olat = self.buf_att[:T * H * r].view(T, H, r)
         groups = 1 if H <= 16 else (H // 16 if H % 16 == 0 else 0)                 # the heads share one key row: 16 of them per CTA
-        if self.use_tiles and groups and r % 8 == 0 and R % 8 == 0 and ld % 8 == 0 and \
+        if self.use_tiles and groups and r % 8 == 0 and R % 8 == 0 and \
                 ops.seq_window_attention_mma_supported(self.dtype, r, R, r, H, groups, False):
             ck = cache[:, :, :r].unsqueeze(2).expand(cache.shape[0], cache.shape[1], groups, r)
             ops.seq_window_attention_mma(qf, ck, cache[:, :, r:], ck, olat, tab, FULL_WINDOW, m.scale, False, gate=gate, gate_per_head=True)
