@@ -5,6 +5,7 @@
 // float32, per-head output norm, and the gated per-token side input. Element type of activations and large weights:
 // bfloat16 or float32; every norm, score, softmax weight, angle, gate of the recurrence and state is float32.
 #include <cstdlib>
+#include <cstring>
 #include "seq_common.cuh"
 #include "../../include/qspec_b200_seq.h"
 
@@ -357,60 +358,95 @@ gated_row_norm_kernel(const float* __restrict__ src, const float* __restrict__ w
 
 // ---- residual sum with a multiplier, and the norm of the next sublayer's input ---------------------------------------
 // r = x_in + mult * (sum of weighted parts of y + weighted y2); out = r / sqrt(mean(r^2) + eps) * (w_offset + w). One CTA per
-// token; the row lives in shared memory between the passes.
-template <typename T, typename YT>
+// token; the row lives in shared memory between the passes. VEC = 4: every thread takes four neighbouring columns with one
+// load per operand (rows and strides on 16-byte boundaries); the parts' weights wait in shared memory.
+template <typename T, typename YT, int VEC>
 __global__ void __launch_bounds__(256)
 residual_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const YT* __restrict__ y, int y_parts,
                      long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w, const YT* __restrict__ y2,
                      const float* __restrict__ y2_w, int y2_w_stride, float mult, const float* __restrict__ w, float w_offset,
                      T* __restrict__ out, int W, float eps) {
   pdl_enter();
-  extern __shared__ float sm_rn[];            // row [W]
+  extern __shared__ __align__(16) float sm_rn[];            // row [W]
   __shared__ float red[8];
+  __shared__ float s_yw[64];
   const int i = blockIdx.x, tid = threadIdx.x;
   const YT* yr = y ? y + (size_t)i * y_tok_stride : nullptr;
   const YT* y2r = y2 ? y2 + (size_t)i * W : nullptr;
   const float w2 = (y2 && y2_w) ? y2_w[(size_t)i * y2_w_stride] : 1.0f;
+  const bool weights_in_smem = y_parts <= 64;
+  if (yr && weights_in_smem) {
+    if (tid < y_parts) s_yw[tid] = y_w ? y_w[(size_t)i * y_parts + tid] : 1.0f;
+    __syncthreads();
+  }
+  const float* xr = x_in + (size_t)i * W;
   float q = 0.f;
-  for (int c = tid; c < W; c += 256) {
-    float v = 0.f;
+  for (int c = tid * VEC; c < W; c += 256 * VEC) {
+    VecF<VEC> v;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v.v[e] = 0.f;
     if (yr) {
-      if (y_parts == 1 && !y_w) v = to_f(yr[c]);
-      else
-        for (int p = 0; p < y_parts; ++p) v += (y_w ? y_w[(size_t)i * y_parts + p] : 1.0f) * to_f(yr[(size_t)p * y_part_stride + c]);
+#pragma unroll 4
+      for (int p = 0; p < y_parts; ++p) {
+        const float wp = weights_in_smem ? s_yw[p] : (y_w ? y_w[(size_t)i * y_parts + p] : 1.0f);
+        const VecF<VEC> t = ldv<VEC>(yr + (size_t)p * y_part_stride + c);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v.v[e] += wp * t.v[e];
+      }
     }
-    if (y2r) v += w2 * to_f(y2r[c]);
-    const float r = x_in[(size_t)i * W + c] + mult * v;
-    if (x_out) x_out[(size_t)i * W + c] = r;
-    sm_rn[c] = r;
-    q += r * r;
+    if (y2r) {
+      const VecF<VEC> t = ldv<VEC>(y2r + c);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v.v[e] += w2 * t.v[e];
+    }
+    VecF<VEC> r = ldv<VEC>(xr + c);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      r.v[e] += mult * v.v[e];
+      q += r.v[e] * r.v[e];
+    }
+    if (x_out) stv<VEC>(x_out + (size_t)i * W + c, r);
+    stv<VEC>(sm_rn + c, r);
   }
   if (!out) return;
   const float rr = 1.0f / sqrtf(block_sum_256(q, red) / (float)W + eps);
-  for (int c = tid; c < W; c += 256) out[(size_t)i * W + c] = from_f<T>(sm_rn[c] * rr * (w_offset + w[c]));
-}
-
-// ---- element-wise activations -------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256) act_kernel(T* __restrict__ a, long long n, int act) {
-  pdl_enter();
-  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
-    const float z = to_f(a[k]);
-    float v;
-    if (act == QSPEC_ACT_GELU_ERF) v = 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
-    else { v = fmaxf(z, 0.f); v *= v; }
-    a[k] = from_f<T>(v);
+  for (int c = tid * VEC; c < W; c += 256 * VEC) {
+    VecF<VEC> r = ldv<VEC>(sm_rn + c);
+    const VecF<VEC> wv = ldv<VEC>(w + c);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) r.v[e] = r.v[e] * rr * (w_offset + wv.v[e]);
+    stv<VEC>(out + (size_t)i * W + c, r);
   }
 }
 
-template <typename T>
+// ---- element-wise activations -------------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_apply(float z, int act) {
+  if (act == QSPEC_ACT_GELU_ERF) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+  const float v = fmaxf(z, 0.f);
+  return v * v;
+}
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) act_kernel(T* __restrict__ a, long long n, int act) {
+  pdl_enter();
+  for (long long k = ((long long)blockIdx.x * 256 + threadIdx.x) * VEC; k < n; k += (long long)gridDim.x * 256 * VEC) {
+    VecF<VEC> v = ldv<VEC>(a + k);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v.v[e] = act_apply(v.v[e], act);
+    stv<VEC>(a + k, v);
+  }
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int F, long long n) {
   pdl_enter();
-  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+  for (long long k = ((long long)blockIdx.x * 256 + threadIdx.x) * VEC; k < n; k += (long long)gridDim.x * 256 * VEC) {
     const long long t = k / F;
     const int f = (int)(k - t * F);
-    const float g = to_f(gu[(size_t)t * ld + f]), u = to_f(gu[(size_t)t * ld + F + f]);
-    out[k] = from_f<T>(g / (1.0f + expf(-g)) * u);
+    const VecF<VEC> g = ldv<VEC>(gu + (size_t)t * ld + f), u = ldv<VEC>(gu + (size_t)t * ld + F + f);
+    VecF<VEC> o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o.v[e] = g.v[e] / (1.0f + expf(-g.v[e])) * u.v[e];
+    stv<VEC>(out + k, o);
   }
 }
 
@@ -778,20 +814,37 @@ extern "C" int qspec_seq_side_gate(void* g, const void* table, const int* ids, i
   return QSPEC_OK;
 }
 
+template <typename T, typename YT, int VEC>
+static int launch_residual_norm_v(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
+                                  const float* y_w, const void* y2, const float* y2_w, int y2_w_stride, float mult, const float* w,
+                                  float w_offset, void* out, int ntok, int W, float eps, cudaStream_t st) {
+  const size_t smem = (size_t)W * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(residual_norm_kernel<T, YT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  launch_pdl(residual_norm_kernel<T, YT, VEC>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const YT*)y, y_parts, y_part_stride,
+             y_tok_stride, y_w, (const YT*)y2, y2_w, y2_w_stride, mult, w, w_offset, (T*)out, W, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
 template <typename T, typename YT>
 static int launch_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
                                 const float* y_w, const void* y2, const float* y2_w, int y2_w_stride, float mult, const float* w,
                                 float w_offset, void* out, int ntok, int W, float eps, cudaStream_t st) {
-  const size_t smem = (size_t)W * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    QSPEC_CUDA(cudaFuncSetAttribute(residual_norm_kernel<T, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
-  launch_pdl(residual_norm_kernel<T, YT>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const YT*)y, y_parts, y_part_stride, y_tok_stride,
-             y_w, (const YT*)y2, y2_w, y2_w_stride, mult, w, w_offset, (T*)out, W, eps);
-  QSPEC_CHECK_LAUNCH(1);
-  return QSPEC_OK;
+  // four columns per thread where every row starts on a 16-byte boundary (float32 rows; bfloat16 rows need 8 bytes)
+  // QSPEC_SEQ_RESNORM=scalar keeps one column per thread and step, for comparison
+  static const bool scalar = [] { const char* v = getenv("QSPEC_SEQ_RESNORM"); return v && !strcmp(v, "scalar"); }();
+  const bool vec = !scalar && W % 4 == 0 && y_part_stride % 4 == 0 && y_tok_stride % 4 == 0 &&
+                   (((uintptr_t)x_in | (uintptr_t)x_out | (uintptr_t)w) & 15) == 0 &&
+                   (((uintptr_t)y | (uintptr_t)y2) & (4 * sizeof(YT) - 1)) == 0 && ((uintptr_t)out & (4 * sizeof(T) - 1)) == 0;
+  if (vec)
+    return launch_residual_norm_v<T, YT, 4>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset,
+                                            out, ntok, W, eps, st);
+  return launch_residual_norm_v<T, YT, 1>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset,
+                                          out, ntok, W, eps, st);
 }
 
 extern "C" int qspec_seq_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
@@ -817,10 +870,18 @@ extern "C" int qspec_seq_act(void* a, long long n, int act, int dtype, void* str
   QSPEC_REQUIRE(act == QSPEC_ACT_RELU2 || act == QSPEC_ACT_GELU_ERF, QSPEC_ERR_INVALID_ARG, "seq_act: unknown activation %d", act);
   MIX_DTYPE_OK(dtype);
   if (n == 0) return QSPEC_OK;
-  long long blocks = (n + 255) / 256;
+  const size_t esz = dtype == QSPEC_DTYPE_F32 ? 4 : 2;
+  const bool vec = n % 4 == 0 && ((uintptr_t)a & (4 * esz - 1)) == 0;
+  long long blocks = (n / (vec ? 4 : 1) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (dtype == QSPEC_DTYPE_F32) launch_pdl(act_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (float*)a, n, act);
-  else launch_pdl(act_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (bf16_t*)a, n, act);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == QSPEC_DTYPE_F32) {
+    if (vec) launch_pdl(act_kernel<float, 4>, dim3((unsigned)blocks), dim3(256), 0, st, (float*)a, n, act);
+    else launch_pdl(act_kernel<float, 1>, dim3((unsigned)blocks), dim3(256), 0, st, (float*)a, n, act);
+  } else {
+    if (vec) launch_pdl(act_kernel<bf16_t, 4>, dim3((unsigned)blocks), dim3(256), 0, st, (bf16_t*)a, n, act);
+    else launch_pdl(act_kernel<bf16_t, 1>, dim3((unsigned)blocks), dim3(256), 0, st, (bf16_t*)a, n, act);
+  }
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
@@ -830,12 +891,18 @@ extern "C" int qspec_seq_silu_mul(const void* gu, int ld, void* out, int ntok, i
   MIX_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   const long long n = (long long)ntok * F;
-  long long blocks = (n + 255) / 256;
+  const size_t esz = dtype == QSPEC_DTYPE_F32 ? 4 : 2;
+  const bool vec = F % 4 == 0 && ld % 4 == 0 && (((uintptr_t)gu | (uintptr_t)out) & (4 * esz - 1)) == 0;
+  long long blocks = (n / (vec ? 4 : 1) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (dtype == QSPEC_DTYPE_F32)
-    launch_pdl(silu_mul_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const float*)gu, ld, (float*)out, F, n);
-  else
-    launch_pdl(silu_mul_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const bf16_t*)gu, ld, (bf16_t*)out, F, n);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == QSPEC_DTYPE_F32) {
+    if (vec) launch_pdl(silu_mul_kernel<float, 4>, dim3((unsigned)blocks), dim3(256), 0, st, (const float*)gu, ld, (float*)out, F, n);
+    else launch_pdl(silu_mul_kernel<float, 1>, dim3((unsigned)blocks), dim3(256), 0, st, (const float*)gu, ld, (float*)out, F, n);
+  } else {
+    if (vec) launch_pdl(silu_mul_kernel<bf16_t, 4>, dim3((unsigned)blocks), dim3(256), 0, st, (const bf16_t*)gu, ld, (bf16_t*)out, F, n);
+    else launch_pdl(silu_mul_kernel<bf16_t, 1>, dim3((unsigned)blocks), dim3(256), 0, st, (const bf16_t*)gu, ld, (bf16_t*)out, F, n);
+  }
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
