@@ -252,6 +252,14 @@ int qspec_moe_route_grouped(const void* h, const float* router_w, const float* c
                             int extra_ld, int ntok, int W, int R, int top, int score_fn, int n_groups, int keep_groups,
                             int group_top, float scale, int n_extra, int dtype, void* stream);
 
+/* Softmax attention of ONE prompt portion on the tensor cores, tile form (bfloat16): the ntok tokens are consecutive positions
+ * pos0 .. pos0 + ntok - 1 of the sequence in slot `slot` (args->meta is not read). A CTA takes 64 tokens and one head and reads
+ * every visible key / value row once, through shared memory. Arguments as for qspec_seq_window_attention_mma (window, sink,
+ * gate, two-part keys); shapes: per-head key part 128 with a shared part of 64 or none and values of 128, or 64 / 64. */
+int qspec_seq_prompt_attention_mma(const qspec_window_attn_args* args, const void* k_shared, long long k_shared_slot_stride,
+                                   int k_shared_row_stride, int DB, int slot, int pos0, void* stream);
+int qspec_seq_prompt_attention_mma_supported(int DA, int DB, int DV);
+
 /* Arg max per row of float32 / bfloat16 logits [rows, V] (lowest index among equal maxima): int64 out. */
 int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,
                           void* stream);

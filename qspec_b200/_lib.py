@@ -159,6 +159,8 @@ SEQ_SIGNATURES = {
     "qspec_seq_silu_mul": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "qspec_seq_lightning": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_prompt_attention_mma": (c_int, [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]),
+    "qspec_seq_prompt_attention_mma_supported": (c_int, [c_int, c_int, c_int]),
     "qspec_moe_route_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
 }

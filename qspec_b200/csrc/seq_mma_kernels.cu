@@ -1432,6 +1432,257 @@ static int launch_latent_absorbed(const WinMma& a, cudaStream_t st) {
   return QSPEC_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Softmax attention of one prompt portion on the tensor cores, tile form: a CTA of four warps takes 64 consecutive tokens
+// of ONE sequence (rows pos0 .. pos0 + ntok - 1 of slot `slot`) and one head, and walks the visible keys in tiles of 64.
+// Key tiles ([per-head part DA | shared part DB]) and value tiles arrive in shared memory by cp.async, two tiles in
+// flight; ldmatrix feeds the fragments (keys as stored, values transposed), so every key / value row is read once per 64
+// queries instead of once per 16. Scores, maxima, sums and weights are float32; the weights enter the second product as a
+// two-term bfloat16 split taken straight from the score accumulators. Causal mask, window, sink and output gate as in
+// window_attn_mma_kernel. CTAs run the longest key ranges first.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <int DA, int DB, int DV, int NW>
+__global__ void __launch_bounds__(32 * NW, NW == 4 ? 2 : 1) prompt_attn_mma_kernel(const WinMma a, int slot, int pos0) {
+  pdl_enter();
+  constexpr int DK = DA + DB, KS = DK + 8, VS = DV + 8, BM = 16 * NW, BN = 64, NT = 32 * NW, TPK = NT / BN;
+  extern __shared__ __align__(16) unsigned char pa_raw[];
+  bf16* sQ = reinterpret_cast<bf16*>(pa_raw);              // [BM][KS]
+  bf16* sK = sQ + BM * KS;                                 // [2][BN][KS]
+  bf16* sV = sK + 2 * BN * KS;                             // [2][BN][VS]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, kvh = head / (a.H / a.G);
+  const int i0 = qb * BM;
+  for (int c = tid; c < BM * (DK / 2); c += NT) {
+    const int row = c / (DK / 2), w = c - row * (DK / 2), tok = i0 + row;
+    uint32_t val = 0u;
+    if (tok < a.ntok) {
+      const float2 f = *reinterpret_cast<const float2*>(a.q + (size_t)tok * a.q_ts + (size_t)head * a.q_hs + 2 * w);
+      val = pack_bf2(f.x, f.y);
+    }
+    *reinterpret_cast<uint32_t*>(sQ + row * KS + 2 * w) = val;
+  }
+  const int last = pos0 + min(i0 + BM, a.ntok) - 1;                     // last key any row of the block sees
+  const int start = max(0, pos0 + i0 - a.window + 1);                    // first key the block's first row sees
+  const int ntiles = (last - start + BN) / BN;
+  const bf16* kA = a.kA + (size_t)slot * a.kA_ss + (size_t)kvh * a.kA_hs;
+  const bf16* kB = DB ? a.kB + (size_t)slot * a.kB_ss : nullptr;
+  const bf16* vb = a.v + (size_t)slot * a.v_ss + (size_t)kvh * a.v_hs;
+  // TPK threads per key row: one row index (position % cap) per thread and tile, then straight runs of 16-byte pieces
+  const int lkey = tid / TPK, lhalf = tid % TPK;
+  auto load_tile = [&](int t, int buf) {
+    const int j = start + t * BN + lkey;
+    const bool ok = j <= last;
+    const int row = ok ? j % a.cap : 0;
+    bf16* dK = sK + ((size_t)buf * BN + lkey) * KS;
+    bf16* dV = sV + ((size_t)buf * BN + lkey) * VS;
+    const bf16* srcA = kA + (size_t)row * a.kA_rs;
+#pragma unroll
+    for (int x = 0; x < DA / 8 / TPK; ++x) {
+      const int ch = lhalf * (DA / 8 / TPK) + x;
+      cp_async16(dK + ch * 8, srcA + ch * 8, ok);
+    }
+    if (DB) {
+      const bf16* srcB = kB + (size_t)row * a.kB_rs;
+#pragma unroll
+      for (int x = 0; x < DB / 8 / TPK; ++x) {
+        const int ch = lhalf * (DB / 8 / TPK) + x;
+        cp_async16(dK + DA + ch * 8, srcB + ch * 8, ok);
+      }
+    }
+    const bf16* srcV = vb + (size_t)row * a.v_rs;
+#pragma unroll
+    for (int x = 0; x < DV / 8 / TPK; ++x) {
+      const int ch = lhalf * (DV / 8 / TPK) + x;
+      cp_async16(dV + ch * 8, srcV + ch * 8, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  load_tile(0, 0);
+  __syncthreads();                                                       // the queries are in shared memory
+  uint32_t qf[DK / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < DK / 16; ++ks)
+    ldmatrix_x4(qf[ks], sQ + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * KS + ks * 16 + 8 * (lane >> 4));
+  float o[DV / 8][4];
+#pragma unroll
+  for (int t = 0; t < DV / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  const int rowA = i0 + warp * 16 + gid, rowB = rowA + 8;
+  const int posA = pos0 + rowA, posB = pos0 + rowB;
+  const int wlast = pos0 + min(i0 + warp * 16 + 15, a.ntok - 1);        // last key this warp's rows see
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) {
+      load_tile(t + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    const int j0 = start + t * BN;
+    if (j0 <= wlast) {                                                   // a tile past this warp's rows holds nothing for it
+      const bf16* K = sK + (size_t)buf * BN * KS;
+      const bf16* V = sV + (size_t)buf * BN * VS;
+      float s[BN / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < DK / 16; ++ks)
+#pragma unroll
+        for (int np = 0; np < BN / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, K + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * KS + ks * 16 + 8 * ((lane >> 3) & 1));
+          mma_bf16_16816(s[2 * np], qf[ks], b[0], b[1]);
+          mma_bf16_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+        }
+      float mxA = -INFINITY, mxB = -INFINITY;
+      // a tile that lies wholly before the warp's first row and inside its last row's window needs no mask (most tiles)
+      const int wfirst = pos0 + i0 + warp * 16;
+      if (j0 + BN - 1 <= wfirst && j0 + BN - 1 <= last && (wfirst + 15) - j0 < a.window) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[nt][c] *= a.scale;
+          mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
+          mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int pj = j0 + nt * 8 + 2 * tig + (c & 1);
+            const int pr = (c >> 1) ? posB : posA;
+            const bool vis = pj <= pr && pr - pj < a.window && pj <= last;
+            s[nt][c] = vis ? s[nt][c] * a.scale : -INFINITY;
+            if (c >> 1) mxB = fmaxf(mxB, s[nt][c]); else mxA = fmaxf(mxA, s[nt][c]);
+          }
+      }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+      const float cA = nA == -INFINITY ? 1.f : __expf(mA - nA), cB = nB == -INFINITY ? 1.f : __expf(mB - nB);
+      const float bA = nA == -INFINITY ? 0.f : nA, bB = nB == -INFINITY ? 0.f : nB;
+      mA = nA; mB = nB;
+      float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        s[nt][0] = __expf(s[nt][0] - bA); s[nt][1] = __expf(s[nt][1] - bA);      // exp(-inf) = 0 for hidden keys
+        s[nt][2] = __expf(s[nt][2] - bB); s[nt][3] = __expf(s[nt][3] - bB);
+        sumA += s[nt][0] + s[nt][1];
+        sumB += s[nt][2] + s[nt][3];
+      }
+      lA = lA * cA + sumA;
+      lB = lB * cB + sumB;
+      if (!__all_sync(0xffffffffu, cA == 1.f && cB == 1.f)) {            // no row of the warp met a new maximum: nothing to rescale
+#pragma unroll
+        for (int t2 = 0; t2 < DV / 8; ++t2) { o[t2][0] *= cA; o[t2][1] *= cA; o[t2][2] *= cB; o[t2][3] *= cB; }
+      }
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+        uint32_t ah[4], al[4];
+        split_bf2(s[2 * kk][0], s[2 * kk][1], ah[0], al[0]);
+        split_bf2(s[2 * kk][2], s[2 * kk][3], ah[1], al[1]);
+        split_bf2(s[2 * kk + 1][0], s[2 * kk + 1][1], ah[2], al[2]);
+        split_bf2(s[2 * kk + 1][2], s[2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+        for (int dp = 0; dp < DV / 16; ++dp) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, V + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * VS + dp * 16 + 8 * (lane >> 4));
+          mma_bf16_16816(o[2 * dp], ah, b[0], b[1]);
+          mma_bf16_16816(o[2 * dp], al, b[0], b[1]);
+          mma_bf16_16816(o[2 * dp + 1], ah, b[2], b[3]);
+          mma_bf16_16816(o[2 * dp + 1], al, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();                                                     // the buffer is free for the tile after next
+  }
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int tok = half ? rowB : rowA;
+    if (tok >= a.ntok) continue;
+    const float m = half ? mB : mA, l = half ? lB : lA;
+    float f = 1.f, L = l;
+    if (a.sink) {
+      const float M = fmaxf(m, a.sink[head]);
+      f = m == -INFINITY ? 0.f : __expf(m - M);
+      L = l * f + __expf(a.sink[head] - M);
+    }
+    float inv = L > 0.f ? f / L : 0.f;
+    const bf16* gp = a.gate ? a.gate + (size_t)tok * a.gate_ld + (a.gate_per_head ? (size_t)head : (size_t)head * DV) : nullptr;
+    if (gp && a.gate_per_head) inv *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(gp[0])));
+    bf16* orow = a.out + ((size_t)tok * a.H + head) * DV;
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+      const int d = nt * 8 + 2 * tig;
+      float v0 = o[nt][2 * half] * inv, v1 = o[nt][2 * half + 1] * inv;
+      if (gp && !a.gate_per_head) {
+        v0 *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(gp[d])));
+        v1 *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(gp[d + 1])));
+      }
+      *reinterpret_cast<uint32_t*>(orow + d) = pack_bf2(v0, v1);
+    }
+  }
+}
+
+template <int DA, int DB, int DV, int NW>
+static int launch_prompt_attn_w(const WinMma& a, int slot, int pos0, cudaStream_t st) {
+  constexpr int BM = 16 * NW;
+  constexpr size_t smem = ((size_t)(BM + 2 * 64) * (DA + DB + 8) + (size_t)2 * 64 * (DV + 8)) * sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(prompt_attn_mma_kernel<DA, DB, DV, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  launch_pdl(prompt_attn_mma_kernel<DA, DB, DV, NW>, dim3((a.ntok + BM - 1) / BM, a.H), dim3(32 * NW), smem, st, a, slot, pos0);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+// 128 tokens per CTA (eight warps, one CTA per SM) once such CTAs fill the GPU: every key / value tile then serves twice the
+// queries; 64 tokens per CTA (two CTAs per SM) for shorter portions. QSPEC_SEQ_PROMPT_ROWS=64 / 128 fixes the choice.
+template <int DA, int DB, int DV>
+static int launch_prompt_attn(const WinMma& a, int slot, int pos0, cudaStream_t st) {
+  static const int fixed = [] { const char* v = getenv("QSPEC_SEQ_PROMPT_ROWS"); return v ? atoi(v) : 0; }();
+  const bool wide = fixed ? fixed == 128 : (long long)((a.ntok + 127) / 128) * a.H >= 148;
+  if (wide) return launch_prompt_attn_w<DA, DB, DV, 8>(a, slot, pos0, st);
+  return launch_prompt_attn_w<DA, DB, DV, 4>(a, slot, pos0, st);
+}
+
+bool prompt_mma_shape(int DA, int DB, int DV) {
+  return (DA == 128 && DB == 64 && DV == 128) || (DA == 128 && DB == 0 && DV == 128) || (DA == 64 && DB == 0 && DV == 64);
+}
+
+// Entry for qspec_seq_prompt_attention_mma (below): -1 when the shape or the strides are not ones this form takes.
+int prompt_attention_mma(const qspec_window_attn_args* p, const void* kB, long long kB_ss, int kB_rs, int DB, int slot, int pos0,
+                         cudaStream_t st) {
+  const int DA = p->DA, DV = p->DV;
+  const bool ok = prompt_mma_shape(DA, DB, DV) && p->H % p->G == 0 && p->H <= 65535 && p->k_row_stride % 8 == 0 && p->k_head_stride % 8 == 0 &&
+                  p->k_slot_stride % 8 == 0 && p->v_row_stride % 8 == 0 && p->v_head_stride % 8 == 0 && p->v_slot_stride % 8 == 0 &&
+                  kB_rs % 8 == 0 && kB_ss % 8 == 0 && p->qa_tok_stride % 2 == 0 && p->qa_head_stride % 2 == 0 &&
+                  (((uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)kB) & 15) == 0 && ((uintptr_t)p->qa & 7) == 0 && ((uintptr_t)p->out & 3) == 0;
+  if (!ok) return -1;
+  WinMma a;
+  a.q = p->qa; a.q_ts = p->qa_tok_stride; a.q_hs = p->qa_head_stride;
+  a.kA = (const bf16*)p->k; a.kA_ss = p->k_slot_stride; a.kA_rs = p->k_row_stride; a.kA_hs = p->k_head_stride;
+  a.kB = (const bf16*)kB; a.kB_ss = kB_ss; a.kB_rs = kB_rs;
+  a.v = (const bf16*)p->v; a.v_ss = p->v_slot_stride; a.v_rs = p->v_row_stride; a.v_hs = p->v_head_stride;
+  a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld; a.gate_per_head = p->gate_per_head;
+  a.out = (bf16*)p->out; a.out_hs = DV; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
+  a.scale = p->scale; a.token_rows = 1;
+  if (DB) return launch_prompt_attn<128, 64, 128>(a, slot, pos0, st);
+  if (DA == 128) return launch_prompt_attn<128, 0, 128>(a, slot, pos0, st);
+  return launch_prompt_attn<64, 0, 64>(a, slot, pos0, st);
+}
+
 template <int DA, int DB, int DV, bool STREAM>
 static int launch_window_mma(const WinMma& a, int slices, cudaStream_t st) {
   constexpr size_t smem = (size_t)16 * ((DA + DB) / 2 + 4) * 4 + (size_t)4 * 16 * DV * sizeof(float);
@@ -1508,3 +1759,20 @@ extern "C" int qspec_seq_window_attention_mma(const qspec_window_attn_args* args
 extern "C" int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int G, int token_rows) {
   return qspec::window_mma_shape(DA, DB, DV) && G > 0 && H % G == 0 && (token_rows || H / G <= 16);
 }
+
+extern "C" int qspec_seq_prompt_attention_mma(const qspec_window_attn_args* args, const void* k_shared, long long k_shared_slot_stride,
+                                              int k_shared_row_stride, int DB, int slot, int pos0, void* stream) {
+  QSPEC_REQUIRE(args && args->qa && args->k && args->v && args->out && (DB == 0 || k_shared), QSPEC_ERR_INVALID_ARG,
+                "seq_prompt_attention_mma: null pointer");
+  QSPEC_REQUIRE(args->DB == 0 && slot >= 0 && pos0 >= 0 && args->window >= 1 && args->cap >= 1, QSPEC_ERR_INVALID_ARG,
+                "seq_prompt_attention_mma: the query is one part here (DA = the whole key size); slot and first position from 0");
+  if (args->ntok == 0) return QSPEC_OK;
+  qspec_window_attn_args p = *args;
+  p.DA = args->DA - DB;
+  const int s = qspec::prompt_attention_mma(&p, k_shared, k_shared_slot_stride, k_shared_row_stride, DB, slot, pos0, (cudaStream_t)stream);
+  QSPEC_REQUIRE(s >= 0, QSPEC_ERR_UNSUPPORTED, "seq_prompt_attention_mma: key parts %d + %d, value size %d, or strides / alignment not taken",
+                args->DA - DB, DB, args->DV);
+  return s;
+}
+
+extern "C" int qspec_seq_prompt_attention_mma_supported(int DA, int DB, int DV) { return qspec::prompt_mma_shape(DA, DB, DV); }

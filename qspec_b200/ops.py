@@ -1209,3 +1209,42 @@ def moe_route_grouped(h: torch.Tensor, router_w: torch.Tensor, correction: Optio
                                                  extra.stride(0) if extra is not None else 0, ntok, W, R, top,
                                                  {"softmax": 0, "sigmoid": 1}[score], int(groups), int(keep), int(group_top),
                                                  float(scale), n_extra, _sdt(h), _stream()), "moe_route_grouped")
+
+
+def seq_prompt_attention_mma_supported(out_dtype, DA: int, DB: int, DV: int) -> bool:
+    """The tile form of a prompt portion takes bfloat16 caches with per-head key parts of 128 (+ a shared part of 64, or none)
+    and values of 128, or keys and values of 64."""
+    return bool(out_dtype == _BF16 and _lib.load_seq().qspec_seq_prompt_attention_mma_supported(DA, DB, DV))
+
+
+def seq_prompt_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: Optional[torch.Tensor], cache_v: torch.Tensor,
+                             out: torch.Tensor, slot: int, pos0: int, window: int, scale: float,
+                             sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                             gate_per_head: bool = False) -> None:
+    """Softmax attention of one prompt portion on the tensor cores (bfloat16): the rows of q [ntok, H, DK] (float32) are the
+    consecutive positions pos0 .. pos0 + ntok - 1 of the sequence in `slot`. 64 tokens and one head per CTA; every visible key /
+    value row is read once per 64 queries. cache_k [slots, cap, G, DA], k_shared [slots, cap, DB] or None (DK = DA + DB), cache_v
+    [slots, cap, G, DV] as for `seq_window_attention_mma`; window, sink, gate likewise."""
+    import ctypes
+    if q.dtype != _F32 or cache_k.dtype != _BF16 or cache_v.dtype != _BF16 or out.dtype != _BF16:
+        raise ValueError("seq_prompt_attention_mma: float32 queries, bfloat16 caches and output")
+    _chk(out, "out", (_BF16,))
+    ntok, H, DK = q.shape
+    slots, cap, G, DA = cache_k.shape
+    DB = k_shared.shape[2] if k_shared is not None else 0
+    DV = cache_v.shape[3]
+    if DK != DA + DB or out.shape != (ntok, H, DV) or cache_v.shape[:3] != (slots, cap, G) or not 0 <= slot < slots \
+            or (k_shared is not None and k_shared.shape[:2] != (slots, cap)) or (gate is not None and gate.dtype != _BF16):
+        raise ValueError("seq_prompt_attention_mma: shapes do not match")
+    for t in (q, cache_k, cache_v, k_shared):
+        if t is not None and t.stride(-1) != 1:
+            raise ValueError("seq_prompt_attention_mma: the last stride must be 1")
+    a = _lib.WindowAttnArgs(q.data_ptr(), q.stride(0), q.stride(1), DK, None, 0, 0, 0,
+                            cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
+                            cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), DV,
+                            _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
+                            _ptr(out), None, ntok, H, G, int(window), cap, float(scale), int(gate_per_head))
+    _seq(_lib.load_seq().qspec_seq_prompt_attention_mma(ctypes.byref(a), k_shared.data_ptr() if k_shared is not None else None,
+                                                        k_shared.stride(0) if k_shared is not None else 0,
+                                                        k_shared.stride(1) if k_shared is not None else 0, DB, int(slot), int(pos0),
+                                                        _stream()), "seq_prompt_attention_mma")

@@ -398,8 +398,14 @@ class RepepelModel(torch.nn.Module):
             # the products cover `rows` rows only; positions below `rows` never wrap, so any ring size >= rows addresses them
             kview = kmat.view(1, rows, H, m.dim).expand(self.n_slots, rows, H, m.dim)
             vview = vmat.view(1, rows, H, m.vdim).expand(self.n_slots, rows, H, m.vdim)
-            ops.seq_window_attention_mma(qf, kview, cache[:, :rows, r:], vview, att, tab, FULL_WINDOW, m.scale, True, gate=gate,
-                                         gate_per_head=True)
+            # 64 tokens per CTA with the keys through shared memory, once the portion fills the GPU with such CTAs; shorter
+            # portions keep 16 tokens per CTA, whose four warps share a block's keys
+            if ((T + 63) // 64) * H >= 256 and ops.seq_prompt_attention_mma_supported(self.dtype, m.dim, R, m.vdim):
+                ops.seq_prompt_attention_mma(qf, kview, cache[:, :rows, r:], vview, att, slot, meta.segments[0][2], FULL_WINDOW, m.scale,
+                                             gate=gate, gate_per_head=True)
+            else:
+                ops.seq_window_attention_mma(qf, kview, cache[:, :rows, r:], vview, att, tab, FULL_WINDOW, m.scale, True, gate=gate,
+                                             gate_per_head=True)
             return att.view(T, H * m.vdim)
         # absorbed form: the query moves into the latent space (W_uk^T q_plain per head, float32) and the cache rows serve as
         # keys and as values; the up-projection of the values follows the attention. The per-head gate is a scalar, so it may

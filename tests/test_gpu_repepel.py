@@ -213,6 +213,43 @@ def test_absorbed_latent_attention_on_the_tensor_cores_with_head_gates(H, groups
     close(out, want, BF16)
 
 
+@pytest.mark.parametrize("DA,DB,DV,H,G", [(128, 64, 128, 3, 3), (128, 0, 128, 4, 2), (64, 0, 64, 2, 1)])
+@pytest.mark.parametrize("pos0,T,window", [(0, 150, FULL), (37, 200, FULL), (130, 64, FULL), (90, 131, 70), (5, 1, FULL)])
+def test_prompt_portion_attention_in_the_tile_form(DA, DB, DV, H, G, pos0, T, window):
+    """64 tokens per CTA over key tiles of 64: portions that start anywhere, end inside a tile, a window that cuts tiles on both
+    sides, a sink, one gate per head or per element; rows past the portion in the caches hold 1e4."""
+    _cuda()
+    from qspec_b200 import ops
+    if not ops.seq_prompt_attention_mma_supported(BF16, DA, DB, DV):
+        pytest.skip("shape not taken by the tile form")
+    g = torch.Generator().manual_seed(DA + DB + pos0 + T)
+    n, scale, cap = pos0 + T, 0.08, 400
+    q = rnd(g, n, H, DA + DB, dtype=BF16, scale=1.0)
+    kA, kB, v = rnd(g, n, G, DA, dtype=BF16), rnd(g, n, max(DB, 1), dtype=BF16), rnd(g, n, G, DV, dtype=BF16)
+    sink = rnd(g, H)
+    rep = H // G
+    k = torch.cat([kA.repeat_interleave(rep, 1), kB.unsqueeze(1).expand(n, H, DB)], -1) if DB else kA.repeat_interleave(rep, 1)
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+    s = s.masked_fill(~((j <= i) & (i - j < window)), float("-inf"))
+    e = torch.exp(s - s.amax(-1, keepdim=True).clamp(min=sink[:, None, None]))
+    wts = e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None, None] - s.amax(-1, keepdim=True).clamp(min=sink[:, None, None])))
+    o = torch.einsum("hij,jhd->ihd", wts, v.repeat_interleave(rep, 1))[pos0:]
+    for per_head in (True, False):
+        gate = rnd(g, T, H + 5 if per_head else H * DV + 8, dtype=BF16, scale=2.0)
+        want = o * (torch.sigmoid(gate[:, :H]).unsqueeze(-1) if per_head else torch.sigmoid(gate[:, :H * DV]).view(T, H, DV))
+        ck = torch.full((2, cap, G, DA), 1e4, dtype=BF16, device="cuda")
+        cs = torch.full((2, cap, max(DB, 8)), 1e4, dtype=BF16, device="cuda")
+        cv = torch.full((2, cap, G, DV), 1e4, dtype=BF16, device="cuda")
+        ck[1, :n], cv[1, :n] = kA.to(BF16).cuda(), v.to(BF16).cuda()
+        if DB:
+            cs[1, :n, :DB] = kB.to(BF16).cuda()
+        out = torch.empty(T, H, DV, dtype=BF16, device="cuda")
+        ops.seq_prompt_attention_mma(q[pos0:].float().cuda(), ck, cs[:, :, :DB] if DB else None, cv, out, 1, pos0, window, scale,
+                                     sink=sink.float().cuda(), gate=gate.to(BF16).cuda(), gate_per_head=per_head)
+        close(out, want, BF16)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("H,D,DV", [(2, 16, 24), (1, 33, 7), (3, 130, 40), (2, 64, 64)])
 def test_linear_attention_state_over_portions_and_slots(dtype, H, D, DV):
