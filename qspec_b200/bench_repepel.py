@@ -123,7 +123,7 @@ def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
             us = _time_us(torch, [lambda i=i: ops.seq_prompt_attention_mma(
                 qfull[i % 2], kmat.view(1, nrows, H, D).expand(nslots, nrows, H, D), lat_cache[i % 2][:, :nrows, kvr:],
                 vmat.view(1, nrows, H, D).expand(nslots, nrows, H, D), oexp, 0, 0, full, 0.07, gate=gate, gate_per_head=True) for i in range(2)])
-            add("seq_prompt_attention_mma, latent expanded form in tiles (64 tokens per CTA, keys through shared memory) + head gate",
+            add("seq_prompt_attention_mma, latent expanded form in tiles (64 or 128 tokens per CTA, keys through shared memory) + head gate",
                 f"T={T} H={H} key {D}+{rot} value {D}", us, flops=2.0 * visible * H * (2 * D + rot))
         else:
             qabs = [torch.randn(T, H, kvr + rot, device=dev) * 0.05 for _ in range(2)]
