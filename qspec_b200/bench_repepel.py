@@ -25,13 +25,13 @@ def repepel_config(s):
     E, F, top = s["moe"]
     count, keep = s["groups"]
     moe = {"kind": "moe", "expert": {"ff": F}, "shared": {"ff": s["shared"]},
-           "router": {"experts": E, "top": top, "scale": 1.5, "groups": {"count": count, "keep": keep}}}
+           "router": {"experts": E, "top": top, "scale": 2.0, "groups": {"count": count, "keep": keep}}}
     dense = {"kind": "dense", "ff": s["ff"]}
     lat = {"heads": H, "dim": D, "vdim": D, "rot_dim": rot, "kv_rank": kvr, "scale": (D + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
     lin = {"heads": H, "dim": D, "vdim": D, "decay": [math.exp(-1.0 / (4.0 * (i + 1))) for i in range(H)]}
     layers = [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
               {"type": "lightning", "mixer": lin, "mlp": moe}]
-    return {"architecture": "Repepel", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+    return {"architecture": "Repepel", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.7,
             "loop": {"start": 0, "stop": 1, "times": 2}, "layers": layers}
 
 
@@ -159,7 +159,7 @@ def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
         idx = torch.empty(T, top, dtype=torch.int32, device=dev)
         wt = torch.empty(T, top, device=dev)
         ex = torch.empty(T, 1, device=dev)
-        us = _time_us(torch, [lambda i=i: ops.moe_route_grouped(hb[i], rwt, corr, idx, wt, groups=count, keep=keep, scale=1.5, extra=ex)
+        us = _time_us(torch, [lambda i=i: ops.moe_route_grouped(hb[i], rwt, corr, idx, wt, groups=count, keep=keep, scale=2.0, extra=ex)
                               for i in range(nbuf)])
         add("moe_route_grouped (sigmoid, groups, shared gate row)", f"{label} T={T} R={E}+1", us, nbytes=T * W * 2)
         gu = [(torch.randn(E, 2 * F, W, device=dev) * W ** -0.5).to(bf) for _ in range(2)]

@@ -331,6 +331,7 @@ class RepepelModel(torch.nn.Module):
         # attention per 16 tokens (prompt portions) or per 16 heads (decoding). QSPEC_SEQ_TILES=0 keeps the plain forms.
         self.use_tiles = dtype == torch.bfloat16 and os.environ.get("QSPEC_SEQ_TILES", "1") != "0"
         self.tiles_min_tokens = 64           # a step with fewer tokens, or fewer than 16 per sequence, is decode-shaped
+        self.prompt_tiles_min_ctas = 256     # (64-token blocks x heads) from which a prompt portion takes the tile form of its attention
         lat_tiles = [m for m in lat if self.use_tiles and m.kv_rank % 8 == 0 and m.rot_dim % 8 == 0 and
                      ops.seq_window_attention_mma_supported(dtype, m.dim, m.rot_dim, m.vdim, m.heads, m.heads, True)]
         self._lat_tiles = {id(m) for m in lat_tiles}
@@ -400,7 +401,7 @@ class RepepelModel(torch.nn.Module):
             vview = vmat.view(1, rows, H, m.vdim).expand(self.n_slots, rows, H, m.vdim)
             # 64 tokens per CTA with the keys through shared memory, once the portion fills the GPU with such CTAs; shorter
             # portions keep 16 tokens per CTA, whose four warps share a block's keys
-            if ((T + 63) // 64) * H >= 256 and ops.seq_prompt_attention_mma_supported(self.dtype, m.dim, R, m.vdim):
+            if ((T + 63) // 64) * H >= self.prompt_tiles_min_ctas and ops.seq_prompt_attention_mma_supported(self.dtype, m.dim, R, m.vdim):
                 ops.seq_prompt_attention_mma(qf, kview, cache[:, :rows, r:], vview, att, slot, meta.segments[0][2], FULL_WINDOW, m.scale,
                                              gate=gate, gate_per_head=True)
             else:

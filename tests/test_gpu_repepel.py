@@ -289,7 +289,7 @@ def test_linear_attention_state_over_portions_and_slots(dtype, H, D, DV):
         close(torch.cat(got), want, dtype)
 
 
-@pytest.mark.parametrize("E,top,count,keep", [(16, 2, 2, 1), (12, 3, 4, 2), (8, 8, 1, 1), (9, 1, 3, 1), (6, 2, 6, 2), (64, 6, 8, 3)])
+@pytest.mark.parametrize("E,top,count,keep", [(20, 3, 2, 1), (12, 3, 4, 2), (8, 8, 1, 1), (9, 1, 3, 1), (6, 2, 6, 2), (64, 6, 8, 3)])
 def test_sigmoid_router_with_expert_groups(E, top, count, keep):
     """Choice = sigmoid score + correction, corrections large and negative enough that choice scores go below zero (a dropped
     group must count as minus infinity, not as zero); weights are the plain scores times the scale; the gate row behind the
@@ -297,7 +297,7 @@ def test_sigmoid_router_with_expert_groups(E, top, count, keep):
     _cuda()
     from qspec_b200 import ops
     g = torch.Generator().manual_seed(E + top)
-    T, W, scale = 40, 48, 1.5
+    T, W, scale = 40, 48, 2.5
     h = rnd(g, T, W)
     rw = rnd(g, E + 1, W, scale=0.3)
     corr = rnd(g, E, scale=0.8) - 1.0
@@ -383,14 +383,14 @@ def dense(ff=40):
     return {"kind": "dense", "ff": ff}
 
 
-def moe(ff=24, experts=6, top=2, count=3, keep=2, scale=1.5, shared=16):
+def moe(ff=24, experts=6, top=2, count=3, keep=2, scale=1.25, shared=16):
     out = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": scale, "groups": {"count": count, "keep": keep}}}
     if shared:
         out["shared"] = {"ff": shared}
     return out
 
 
-def config(layers, width=64, vocab=97, eps=1e-5, mult=0.5, loop=None):
+def config(layers, width=64, vocab=97, eps=1e-5, mult=0.6, loop=None):
     out = {"architecture": "Repepel", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": mult,
            "layers": [dict(l, mlp=l.get("mlp")) for l in layers]}
     if loop:
@@ -426,6 +426,13 @@ def build(name, dtype, seed=0, n_slots=3, max_step_tokens=64, max_seq_tokens=256
     from qspec_b200.scheduler import Scheduler
     cfg = RepepelConfig.from_dict(CONFIGS[name])
     w = random_weights(cfg, seed)
+    if dtype == BF16:
+        # corrections eight times as wide: the experts' choice scores lie far apart, so that bfloat16 rounding rarely flips a
+        # choice (a flip replaces a token's whole feed-forward output and, through the linear-attention state, moves every later
+        # position); routing that follows the input closely is what the float32 runs cover
+        for k in w:
+            if k.endswith("mlp.correction"):
+                w[k] = (w[k].float() * 8.0).to(BF16)
     model = RepepelModel(cfg, w, dtype=dtype, device="cuda", n_slots=n_slots, max_step_tokens=max_step_tokens, max_seq_tokens=max_seq_tokens)
     return CONFIGS[name], w, model, Scheduler(model)
 
@@ -434,25 +441,41 @@ def tokens(n, vocab, seed):
     return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
 
 
-def close_logits(got, ref, dtype):
+def close_logits(got, ref, dtype, same_format=False):
     """Per position: root mean square over the vocabulary of the difference (mean taken off), relative to the spread of the
-    logits. float32 must sit at rounding level; bfloat16 within what its 8-bit mantissa leaves after a few layers, where a
-    router choice may flip on a near tie with random weights (few positions far off)."""
+    logits. float32 against the plain implementation: rounding level. bfloat16 against the plain implementation: what an 8-bit
+    mantissa leaves after up to eight layer runs at width 64 (measured: 0.6 to 1.6 % at the median position; a wrong cache row
+    or a lost state puts the median near 1), with few positions far off where a router choice still flips. same_format:
+    bfloat16 against bfloat16 logits of the same model fed another way -- the same kernels per token agree to float32
+    rounding of the logits; where the step's shape selects another kernel form, to bfloat16 rounding."""
     ref = ref.to(F64)
     d = got.detach().cpu().to(F64) - ref
     d = d - d.mean(-1, keepdim=True)
     spread = float((ref - ref.mean(-1, keepdim=True)).pow(2).mean().sqrt())
     rows = d.pow(2).mean(-1).sqrt() / spread
     if dtype == F32:
-        # rounding level at the typical position; the worst may be a token whose linear-attention output is tiny before its norm
-        # (q.k of the first token cancels to 1e-3 of its terms with some seeds), which multiplies float32 rounding by 1e3
+        # the worst may be a token whose linear-attention output is tiny before its norm (q.k of the first token cancels to
+        # 1e-3 of its terms with some seeds), which multiplies float32 rounding by 1e3
         assert float(rows.median()) <= 1e-5, f"median position: {float(rows.median()):.3g} of the logits' spread"
         assert float(rows.max()) <= 3e-4, f"worst position: {float(rows.max()):.3g} of the logits' spread"
         return
-    # (eight layer runs at width 64: a wrong cache row or a lost state puts the median near 1)
     over = float((rows > 0.1).float().mean())
-    assert float(rows.median()) <= 3e-2, f"median position: {float(rows.median()):.3g} of the logits' spread"
-    assert over <= 0.15, f"{over:.1%} of the positions are off by more than 10% of the logits' spread"
+    bound = 1.5e-2 if same_format else 2.5e-2
+    assert float(rows.median()) <= bound, f"median position: {float(rows.median()):.3g} of the logits' spread"
+    assert over <= 0.1, f"{over:.1%} of the positions are off by more than 10% of the logits' spread"
+
+
+def reference_logits(name, cfg, w, toks, dtype):
+    """float32: the plain implementation. bfloat16: the same weights in a second model that takes the prompt whole, after that
+    has been held against the plain implementation."""
+    ref = O.forward(cfg, w, toks)
+    if dtype == F32:
+        return ref
+    _, _, _, s = build(name, dtype, max_step_tokens=256)
+    whole = s.feed([("whole", toks, list(range(len(toks))))]).float().cpu()
+    if len(toks) >= 8:                                      # a handful of positions has no typical one
+        close_logits(whole, ref, dtype)
+    return whole
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -480,7 +503,7 @@ def test_decoding_and_portions_equal_the_whole_prompt(name, dtype):
     longer than the model's step size (cut inside the step function)."""
     cfg, w, model, s = build(name, dtype, max_step_tokens=16)
     toks = tokens(75, cfg["vocab"], 2)
-    ref = O.forward(cfg, w, toks)
+    ref = reference_logits(name, cfg, w, toks, dtype)
     schedules = {"single": [1] * len(toks), "prompt+decode": [16, 16, 3] + [1] * 40, "portions": [2, 3, 1, 7, 2, 2, 13, 5, 2, 16, 14, 8],
                  "one step": [len(toks)]}
     for label, cuts in schedules.items():
@@ -490,7 +513,7 @@ def test_decoding_and_portions_equal_the_whole_prompt(name, dtype):
             rows.append(s.feed([(label, toks[at:at + n], list(range(n)))]))
             at += n
         s.release(label)
-        close_logits(torch.cat(rows), ref, dtype)
+        close_logits(torch.cat(rows), ref, dtype, same_format=True)
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -522,12 +545,12 @@ def test_mixed_batches_equal_each_request_alone_and_slots_are_reused(dtype):
             live.remove(k)
             s.release(k)
         step += 1
-    refs = {k: O.forward(cfg, w, toks) for k, toks in reqs.items()}
+    refs = {k: reference_logits("mixed", cfg, w, toks, dtype) for k, toks in reqs.items()}
     if dtype == F32:
         for k in reqs:
             close_logits(torch.cat(got[k]), refs[k], dtype)
     else:                                                   # a request of two tokens has no typical position: all rows together
-        close_logits(torch.cat([torch.cat(got[k]) for k in reqs]), torch.cat([refs[k] for k in reqs]), dtype)
+        close_logits(torch.cat([torch.cat(got[k]) for k in reqs]), torch.cat([refs[k] for k in reqs]), dtype, same_format=True)
 
 
 def test_batch_composition_changes_nothing_in_float32():
@@ -556,6 +579,25 @@ def test_prompt_and_decode_forms_on_the_tensor_cores_match_the_plain_implementat
     close_logits(torch.cat(rows), ref, BF16)
     from qspec_b200 import ops
     assert ops.moe_grouped_status() == 0
+
+
+def test_prompt_portions_in_the_tile_form_inside_the_model():
+    """The same model with the tile form of the prompt attention switched on for short portions: a first portion, a second one
+    that starts inside a key tile, then decoding; against the plain implementation and against the 16-token form."""
+    cfg, w, model, s = build("tiles", BF16, n_slots=2, max_step_tokens=160, max_seq_tokens=512)
+    toks = tokens(230, cfg["vocab"], 11)
+    ref = O.forward(cfg, w, toks)
+    outs = {}
+    for label, ctas in (("tiles", 1), ("rows16", 1 << 30)):
+        model.prompt_tiles_min_ctas = ctas
+        rows = [s.feed([(label, toks[:130], list(range(130)))]), s.feed([(label, toks[130:210], list(range(80)))])]
+        rows += [s.feed([(label, [t], [0])]) for t in toks[210:]]
+        s.release(label)
+        outs[label] = torch.cat(rows)
+        close_logits(outs[label], ref, BF16)
+    d = (outs["tiles"] - outs["rows16"]).float()
+    spread = float((ref - ref.mean(-1, keepdim=True)).pow(2).mean().sqrt())
+    assert float(d.pow(2).mean(-1).sqrt().median()) <= 1e-2 * spread
 
 
 def test_the_cache_bounds_the_sequence_and_the_scheduler_refuses_more():

@@ -18,7 +18,7 @@ MOE = {"kind": "moe", "expert": {"ff": 12}, "shared": {"ff": 9},
        "router": {"experts": 6, "top": 2, "scale": 1.25, "groups": {"count": 3, "keep": 2}}}
 
 
-def _cfg(layers, loop=None, width=32, vocab=41, mult=0.5):
+def _cfg(layers, loop=None, width=32, vocab=41, mult=0.6):
     out = {"architecture": "Repepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": mult, "layers": layers}
     if loop:
         out["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
