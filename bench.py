@@ -49,7 +49,7 @@ def parse():
                          "decoder at equal sizes; pitudra: the same for the Pitudra design next to Mutusun "
                          "(qspec_b200/bench_seq.py); repepel: the same for the Repepel design next to Pitudra "
                          "(qspec_b200/bench_repepel.py); the default workload is unchanged")
-    ap.add_argument("--sizes", default="", help="--design mutusun / pitudra: comma-separated size names (default: all)")
+    ap.add_argument("--sizes", default="", help="--design mutusun / pitudra / repepel: comma-separated size names (default: all)")
     a = ap.parse_args()
     if a.seqs is None:
         a.seqs = 32 if a.model == "70b" else 64
