@@ -260,6 +260,76 @@ int qspec_seq_prompt_attention_mma(const qspec_window_attn_args* args, const voi
                                    int k_shared_row_stride, int DB, int slot, int pos0, void* stream);
 int qspec_seq_prompt_attention_mma_supported(int DA, int DB, int DV);
 
+/* ---- mixers whose state is a matrix that every token rewrites, attention with mixed heads, layer scale ---- */
+
+/* qspec_seq_residual_norm with one factor per column on the sublayer's result (a layer scale; NULL: ones):
+ *   r = x_in + mult * y_scale * (sum of the weighted parts of y + y2_w * y2). */
+int qspec_seq_residual_norm_scaled(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                   long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
+                                   float mult, const float* y_scale, const float* w, float w_offset, void* out, int ntok, int W,
+                                   float eps, int y_dtype, int dtype, void* stream);
+
+/* Short causal convolution over time with an activation: out[t, c] = act(bias[c] + sum_j w[c, j] * in[t - taps + 1 + j, c]),
+ * in [ntok, ld] (the first C columns), w float32 [C, taps] (the last column meets the current token), bias float32 [C] or NULL.
+ * Rows before a segment's first token come from tail: float32 [2][slots][taps - 1][C]; the step reads buffer `phase` and writes
+ * buffer `1 - phase` with the sequence's last taps - 1 inputs. Rows before position 0 are zero. out [ntok, out_ld] is float32
+ * if out_f32, else of the activation type. taps <= 64. */
+#define QSPEC_CONV_ACT_NONE 0
+#define QSPEC_CONV_ACT_SILU 1
+int qspec_seq_conv_act(const void* in, int ld, const float* w, const float* bias, int C, int taps, int act, float* tail, int slots,
+                       void* out, int out_ld, int out_f32, const int* meta, int ntok, int dtype, void* stream);
+
+/* Gated delta rule. Row t of cs (float32, leading dimension ld, changed in place): [q (G x D) | k (G x D) | v (H x DV)], after
+ * convolution and activation. q <- q / sqrt(sum q^2 + unit_eps) * q_mult, k <- k / sqrt(sum k^2 + unit_eps). ba float32
+ * [ntok, 2 H] = [b | a]: beta = sigmoid(b), g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])). Per head h with the query / key
+ * head h / (H / G) and S float32 [D, DV]:   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+ * out[t, h] = o / sqrt(mean(o^2) + eps) * norm_w * silu(gate[t, h * DV + c]) (gate of the activation type, leading dimension
+ * gate_ld; NULL: no gate). state: float32 [slots, H, D, DV], read at a segment's start (zero at position 0), written at its
+ * end. Scratch: gates float32 [ntok, 2 H + G], o float32 [ntok, H, DV]. seg_starts int32 [nseg]: the batch row of every
+ * segment's first token. D <= 256. */
+int qspec_seq_delta_rule(float* cs, int ld, const float* ba, const float* A_log, const float* dt_bias, const float* norm_w,
+                         const void* gate, int gate_ld, float* state, float* gates, float* o, void* out, const int* meta,
+                         const int* seg_starts, int nseg, int ntok, int H, int G, int D, int DV, float unit_eps, float q_mult, float eps,
+                         int dtype, void* stream);
+
+/* Selective scan. Per channel c and state n, with dt = softplus(dt_pre[t, c] + dt_bias[c]) and A = -exp(A_log[c, n]):
+ *   S[c, n] <- exp(dt A) S[c, n] + dt x[t, c] B[t, n];   y = sum_n S[c, n] C[t, n] + D_skip[c] x[t, c];   out = y * silu(z[t, c]).
+ * x, z, out and bc (row [B (N) | C (N)]) are of the activation type with their leading dimensions; dt_pre float32. state: float32
+ * [slots, inner, N], read at a segment's start (zero at position 0), written at its end. N <= 512. */
+int qspec_seq_selective_scan(const void* x, int x_ld, const float* dt_pre, int dt_ld, const float* dt_bias, const void* bc, int bc_ld,
+                             const void* z, int z_ld, const float* A_log, const float* D_skip, float* state, void* out, int out_ld,
+                             const int* meta, const int* seg_starts, int nseg, int ntok, int inner, int N, int dtype, void* stream);
+
+/* Grouped-query attention, after the fused projection (biases added): row t of p = [q (H x D) | k (G x D) | v (G x DV)]. Per
+ * head: q, k <- unit_rms over D * weight (qn_w / kn_w, D entries, the same for every head), then the first rot_dims entries are
+ * rotated, entry i with entry i + rot_dims / 2 by the angle pos * inv_freq[i] (float32). v <- unit_rms over DV if v_norm. With
+ * v_first_in (float32 [ntok, G, DV]): v <- (1 - mix[0]) v + mix[0] v_first_in; otherwise v_first_out, if given, receives v.
+ * qout float32 [ntok, H, D]; cache_k [slots, cap, G, D] and cache_v [slots, cap, G, DV] take row pos % cap. */
+int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, const float* kn_w, const float* inv_freq, int rot_dims,
+                       const float* v_first_in, float* v_first_out, const float* mix, float* qout, void* cache_k, void* cache_v, int cap,
+                       const int* meta, int ntok, int H, int G, int D, int DV, float eps, int v_norm, int dtype, void* stream);
+
+/* Softmax attention whose heads' weights are mixed after the softmax. Token at position i sees keys j with 0 <= i - j < window.
+ * weight_g(j) = exp(s_g(j)) / (exp(sink[g]) + sum_j exp(s_g(j))), s = scale * q_g . key of g's key/value head (sink NULL: no such
+ * term); head h applies sum_g talk[h, g] weight_g(j) to the values of its own key/value head h / (H / G). q float32 [ntok, H, D];
+ * keys and values as rows of per-slot rings with element strides, as for qspec_seq_window_attention; talk float32 [H, H];
+ * out [ntok, H, DV]. H * DV <= 16384. */
+typedef struct qspec_talking_attn_args {
+  const float* q;
+  const void* k; long long k_slot_stride; int k_row_stride, k_head_stride;
+  const void* v; long long v_slot_stride; int v_row_stride, v_head_stride;
+  const float* talk; const float* sink;
+  void* out; const int* meta; int ntok, H, G, D, DV, window, cap; float scale;
+} qspec_talking_attn_args;
+int qspec_seq_talking_attention(const qspec_talking_attn_args* args, int dtype, void* stream);
+
+/* out[t, f] = g * sigmoid(alpha g) * (u + 1), g = min(gu[t, f], limit), u = clamp(gu[t, F + f], -limit, limit): rows of gu are
+ * [gate (F) | up (F)] with leading dimension ld; out [ntok, F]. */
+int qspec_seq_glu_clamp(const void* gu, int ld, void* out, int ntok, int F, float limit, float alpha, int dtype, void* stream);
+
+/* a <- s * a, n float32 values. */
+int qspec_seq_scale_f32(float* a, long long n, float s, void* stream);
+
 /* Arg max per row of float32 / bfloat16 logits [rows, V] (lowest index among equal maxima): int64 out. */
 int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,
                           void* stream);

@@ -163,6 +163,23 @@ SEQ_SIGNATURES = {
     "qspec_seq_prompt_attention_mma_supported": (c_int, [c_int, c_int, c_int]),
     "qspec_moe_route_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]),
+    "qspec_seq_residual_norm_scaled": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_float, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_int, c_int,
+                                               c_void_p]),
+    "qspec_seq_conv_act": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                   c_void_p, c_int, c_int, c_void_p]),
+    "qspec_seq_delta_rule": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                     c_float, c_int, c_void_p]),
+    "qspec_seq_selective_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p]),
+    "qspec_seq_gqa_prep": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                   c_void_p]),
+    "qspec_seq_talking_attention": (c_int, [c_void_p, c_int, c_void_p]),
+    "qspec_seq_glu_clamp": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "qspec_seq_scale_f32": (c_int, [c_void_p, c_ll, c_float, c_void_p]),
 }
 
 
@@ -175,6 +192,18 @@ class WindowAttnArgs(ctypes.Structure):
                 ("sink", c_void_p), ("gate", c_void_p), ("gate_ld", c_int),
                 ("out", c_void_p), ("meta", c_void_p), ("ntok", c_int), ("H", c_int), ("G", c_int), ("window", c_int),
                 ("cap", c_int), ("scale", c_float), ("gate_per_head", c_int)]
+
+
+
+class TalkingAttnArgs(ctypes.Structure):
+    """qspec_talking_attn_args of include/qspec_b200_seq.h."""
+    _fields_ = [("q", c_void_p),
+                ("k", c_void_p), ("k_slot_stride", c_ll), ("k_row_stride", c_int), ("k_head_stride", c_int),
+                ("v", c_void_p), ("v_slot_stride", c_ll), ("v_row_stride", c_int), ("v_head_stride", c_int),
+                ("talk", c_void_p), ("sink", c_void_p),
+                ("out", c_void_p), ("meta", c_void_p), ("ntok", c_int), ("H", c_int), ("G", c_int), ("D", c_int), ("DV", c_int),
+                ("window", c_int), ("cap", c_int), ("scale", c_float)]
+
 
 _lib = None
 _seq_lib = None

@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(OUT_DIR, "libqspec_b200.so")
 SOURCES = ["capi.cu", "act_kernels.cu", "hadamard_kernels.cu", "gemm_w4_stream.cu", "attn_kernels.cu", "qwen_kernels.cu"]
 # The sequence-mixer kernels (include/qspec_b200_seq.h) are a library of their own, so that a model that needs only them
 # builds only them: libqspec_b200_seq.so.
-SEQ_SOURCES = ["capi.cu", "seq_kernels.cu", "seq_mma_kernels.cu", "seq_mix_kernels.cu"]
+SEQ_SOURCES = ["capi.cu", "seq_kernels.cu", "seq_mma_kernels.cu", "seq_mix_kernels.cu", "seq_state_kernels.cu"]
 SEQ_LIB_PATH = os.path.join(OUT_DIR, "libqspec_b200_seq.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]

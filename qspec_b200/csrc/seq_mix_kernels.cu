@@ -357,7 +357,7 @@ gated_row_norm_kernel(const float* __restrict__ src, const float* __restrict__ w
 }
 
 // ---- residual sum with a multiplier, and the norm of the next sublayer's input ---------------------------------------
-// r = x_in + mult * (sum of weighted parts of y + weighted y2); out = r / sqrt(mean(r^2) + eps) * (w_offset + w). One CTA per
+// r = x_in + mult * y_scale * (sum of weighted parts of y + weighted y2); out = r / sqrt(mean(r^2) + eps) * (w_offset + w). One CTA per
 // token; the row lives in shared memory between the passes. VEC = 4: every thread takes four neighbouring columns with one
 // load per operand (rows and strides on 16-byte boundaries); the parts' weights wait in shared memory.
 template <typename T, typename YT, int VEC>
@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(256)
 residual_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const YT* __restrict__ y, int y_parts,
                      long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w, const YT* __restrict__ y2,
                      const float* __restrict__ y2_w, int y2_w_stride, float mult, const float* __restrict__ w, float w_offset,
-                     T* __restrict__ out, int W, float eps) {
+                     T* __restrict__ out, int W, float eps, const float* __restrict__ y_scale) {
   pdl_enter();
   extern __shared__ __align__(16) float sm_rn[];            // row [W]
   __shared__ float red[8];
@@ -398,6 +398,11 @@ residual_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, 
       const VecF<VEC> t = ldv<VEC>(y2r + c);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) v.v[e] += w2 * t.v[e];
+    }
+    if (y_scale) {                                          // one factor per column (a layer scale)
+      const VecF<VEC> sc = ldv<VEC>(y_scale + c);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v.v[e] *= sc.v[e];
     }
     VecF<VEC> r = ldv<VEC>(xr + c);
 #pragma unroll
@@ -817,7 +822,7 @@ extern "C" int qspec_seq_side_gate(void* g, const void* table, const int* ids, i
 template <typename T, typename YT, int VEC>
 static int launch_residual_norm_v(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
                                   const float* y_w, const void* y2, const float* y2_w, int y2_w_stride, float mult, const float* w,
-                                  float w_offset, void* out, int ntok, int W, float eps, cudaStream_t st) {
+                                  float w_offset, void* out, int ntok, int W, float eps, const float* y_scale, cudaStream_t st) {
   const size_t smem = (size_t)W * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
@@ -825,7 +830,7 @@ static int launch_residual_norm_v(const float* x_in, float* x_out, const void* y
     configured = smem;
   }
   launch_pdl(residual_norm_kernel<T, YT, VEC>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const YT*)y, y_parts, y_part_stride,
-             y_tok_stride, y_w, (const YT*)y2, y2_w, y2_w_stride, mult, w, w_offset, (T*)out, W, eps);
+             y_tok_stride, y_w, (const YT*)y2, y2_w, y2_w_stride, mult, w, w_offset, (T*)out, W, eps, y_scale);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
@@ -833,24 +838,24 @@ static int launch_residual_norm_v(const float* x_in, float* x_out, const void* y
 template <typename T, typename YT>
 static int launch_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
                                 const float* y_w, const void* y2, const float* y2_w, int y2_w_stride, float mult, const float* w,
-                                float w_offset, void* out, int ntok, int W, float eps, cudaStream_t st) {
+                                float w_offset, void* out, int ntok, int W, float eps, const float* y_scale, cudaStream_t st) {
   // four columns per thread where every row starts on a 16-byte boundary (float32 rows; bfloat16 rows need 8 bytes)
   // QSPEC_SEQ_RESNORM=scalar keeps one column per thread and step, for comparison
   static const bool scalar = [] { const char* v = getenv("QSPEC_SEQ_RESNORM"); return v && !strcmp(v, "scalar"); }();
   const bool vec = !scalar && W % 4 == 0 && y_part_stride % 4 == 0 && y_tok_stride % 4 == 0 &&
-                   (((uintptr_t)x_in | (uintptr_t)x_out | (uintptr_t)w) & 15) == 0 &&
+                   (((uintptr_t)x_in | (uintptr_t)x_out | (uintptr_t)w | (uintptr_t)y_scale) & 15) == 0 &&
                    (((uintptr_t)y | (uintptr_t)y2) & (4 * sizeof(YT) - 1)) == 0 && ((uintptr_t)out & (4 * sizeof(T) - 1)) == 0;
   if (vec)
     return launch_residual_norm_v<T, YT, 4>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset,
-                                            out, ntok, W, eps, st);
+                                            out, ntok, W, eps, y_scale, st);
   return launch_residual_norm_v<T, YT, 1>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset,
-                                          out, ntok, W, eps, st);
+                                          out, ntok, W, eps, y_scale, st);
 }
 
-extern "C" int qspec_seq_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
-                                       long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
-                                       float mult, const float* w, float w_offset, void* out, int ntok, int W, float eps, int y_dtype,
-                                       int dtype, void* stream) {
+extern "C" int qspec_seq_residual_norm_scaled(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                              long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
+                                              float mult, const float* y_scale, const float* w, float w_offset, void* out, int ntok, int W,
+                                              float eps, int y_dtype, int dtype, void* stream) {
   QSPEC_REQUIRE(x_in && (x_out || out) && (!out || w), QSPEC_ERR_INVALID_ARG, "seq_residual_norm: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && W > 0 && W <= 49152 && y_parts >= 1 && y2_w_stride >= 0, QSPEC_ERR_INVALID_ARG,
                 "seq_residual_norm: bad sizes (width <= 49152)");
@@ -858,11 +863,19 @@ extern "C" int qspec_seq_residual_norm(const float* x_in, float* x_out, const vo
   QSPEC_REQUIRE(y_dtype == dtype || y_dtype == QSPEC_DTYPE_F32, QSPEC_ERR_UNSUPPORTED, "seq_residual_norm: y is of the activation type or float32");
   if (ntok == 0) return QSPEC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-#define RN_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset, out, ntok, W, eps, st
+#define RN_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, w, w_offset, out, ntok, W, eps, y_scale, st
   if (dtype == QSPEC_DTYPE_F32) return launch_residual_norm<float, float>(RN_ARGS);
   if (y_dtype == QSPEC_DTYPE_F32) return launch_residual_norm<bf16_t, float>(RN_ARGS);
   return launch_residual_norm<bf16_t, bf16_t>(RN_ARGS);
 #undef RN_ARGS
+}
+
+extern "C" int qspec_seq_residual_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                       long long y_tok_stride, const float* y_w, const void* y2, const float* y2_w, int y2_w_stride,
+                                       float mult, const float* w, float w_offset, void* out, int ntok, int W, float eps, int y_dtype,
+                                       int dtype, void* stream) {
+  return qspec_seq_residual_norm_scaled(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, y2, y2_w, y2_w_stride, mult, nullptr, w,
+                                        w_offset, out, ntok, W, eps, y_dtype, dtype, stream);
 }
 
 extern "C" int qspec_seq_act(void* a, long long n, int act, int dtype, void* stream) {

@@ -1112,8 +1112,9 @@ def seq_side_gate(g: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0:
 def seq_residual_norm(x_in: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, y: Optional[torch.Tensor] = None,
                       y_w: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None, y2_w: Optional[torch.Tensor] = None,
                       mult: float = 1.0, w_offset: float = 1.0, x_out: Optional[torch.Tensor] = None,
-                      out: Optional[torch.Tensor] = None) -> None:
-    """r = x_in + mult * (sum of y's parts, each times y_w [ntok, parts] if given, + y2_w * y2); out = r / rms(r) * (w_offset + w).
+                      out: Optional[torch.Tensor] = None, y_scale: Optional[torch.Tensor] = None) -> None:
+    """r = x_in + mult * y_scale * (sum of y's parts, each times y_w [ntok, parts] if given, + y2_w * y2); out = r / rms(r) *
+    (w_offset + w). y_scale: float32 [W], one factor per column (a layer scale), None: ones.
     y [ntok, W] or [ntok, parts, W]; y2 [ntok, W] with one weight per token (y2_w: a float32 vector view, any stride). r goes to
     x_out (float32; may be x_in), the norm to out (activation type). w_offset 1: the weight is stored around zero; 0: plain."""
     _chk(x_in, "x_in", (_F32,)); _chk(w, "w", (_F32,), allow_none=out is None); _chk(x_out, "x_out", (_F32,), allow_none=True)
@@ -1137,15 +1138,16 @@ def seq_residual_norm(x_in: torch.Tensor, w: Optional[torch.Tensor], eps: float,
     for t in (x_out, out):
         if t is not None and t.shape != (ntok, W):
             raise ValueError("seq_residual_norm: shapes do not match")
-    if w is not None and w.numel() != W:
-        raise ValueError("seq_residual_norm: the norm weight has W entries")
+    _chk(y_scale, "y_scale", (_F32,), allow_none=True)
+    if (w is not None and w.numel() != W) or (y_scale is not None and y_scale.numel() != W):
+        raise ValueError("seq_residual_norm: the norm weight and the column factors have W entries")
     src = y if y is not None else y2
     act = _sdt(out) if out is not None else (_sdt(src) if src is not None and src.dtype != _F32 else _lib.DTYPE_F32)
     ydt = _sdt(src) if src is not None else act
-    _seq(_lib.load_seq().qspec_seq_residual_norm(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(y2),
-                                                 y2_w.data_ptr() if y2_w is not None else None, w2_stride, float(mult), _ptr(w),
-                                                 float(w_offset), _ptr(out), ntok, W, float(eps), ydt, act, _stream()),
-         "seq_residual_norm")
+    _seq(_lib.load_seq().qspec_seq_residual_norm_scaled(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(y2),
+                                                        y2_w.data_ptr() if y2_w is not None else None, w2_stride, float(mult),
+                                                        _ptr(y_scale), _ptr(w), float(w_offset), _ptr(out), ntok, W, float(eps), ydt,
+                                                        act, _stream()), "seq_residual_norm")
 
 
 SEQ_ACTS = {"relu2": 0, "gelu_erf": 1}                 # QSPEC_ACT_* of include/qspec_b200_seq.h
@@ -1248,3 +1250,147 @@ def seq_prompt_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: O
                                                         k_shared.stride(0) if k_shared is not None else 0,
                                                         k_shared.stride(1) if k_shared is not None else 0, DB, int(slot), int(pos0),
                                                         _stream()), "seq_prompt_attention_mma")
+
+
+# ---- mixers whose state is a matrix that every token rewrites; attention with mixed heads ---------------------------------------
+def _rows(t: torch.Tensor, name: str, dtypes) -> None:
+    """A CUDA matrix view whose rows are contiguous (any leading dimension)."""
+    if t is None or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype not in dtypes:
+        raise ValueError(f"{name}: a CUDA matrix of {dtypes} with a unit last stride expected")
+
+
+CONV_ACTS = {None: 0, "none": 0, "silu": 1}            # QSPEC_CONV_ACT_* of include/qspec_b200_seq.h
+
+
+def seq_conv_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, out: torch.Tensor,
+                 meta: torch.Tensor, act: Optional[str] = "silu") -> None:
+    """Short causal convolution per channel with an activation. x [ntok, C] (a view with any leading dimension), w float32
+    [C, taps] (the last column meets the current token), bias float32 [C] or None, tail float32 [2, slots, taps - 1, C] (the
+    sequences' last inputs, double-buffered by the step's phase), out [ntok, C] (view) of x's type or float32."""
+    _rows(x, "x", _SEQ_ACT); _rows(out, "out", (x.dtype, _F32))
+    _chk(w, "w", (_F32,)); _chk(bias, "bias", (_F32,), allow_none=True); _chk(tail, "tail", (_F32,))
+    ntok, C = x.shape
+    taps = w.shape[1]
+    if w.shape[0] != C or out.shape != (ntok, C) or tail.dim() != 4 or tail.shape[0] != 2 or tail.shape[2:] != (taps - 1, C) or \
+            (bias is not None and bias.numel() != C) or meta.shape != (5, ntok):
+        raise ValueError("seq_conv_act: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_conv_act(x.data_ptr(), x.stride(0), _ptr(w), _ptr(bias), C, taps, CONV_ACTS[act], _ptr(tail),
+                                            tail.shape[1], out.data_ptr(), out.stride(0), int(out.dtype == _F32 and x.dtype != _F32),
+                                            _ptr(meta), ntok, _sdt(x), _stream()), "seq_conv_act")
+
+
+def seq_delta_rule(cs: torch.Tensor, ba: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor,
+                   gate: Optional[torch.Tensor], state: torch.Tensor, gates: torch.Tensor, o: torch.Tensor, out: torch.Tensor,
+                   meta: torch.Tensor, seg_starts: torch.Tensor, H: int, G: int, D: int, DV: int, eps: float, unit_eps: float = 1e-6,
+                   q_mult: Optional[float] = None) -> None:
+    """Gated delta rule over rows cs = [q (G x D) | k (G x D) | v (H x DV)] (float32, after convolution and activation; q and k
+    are made unit vectors in place, q times q_mult, default D^-1/2). ba float32 [ntok, 2 H] = [b | a]: beta = sigmoid(b), decay =
+    exp(-exp(A_log) softplus(a + dt_bias)). Per head S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out [ntok, H *
+    DV] = unit_rms(o) * norm_w * silu(gate) (gate [ntok, H * DV] view of out's type, or None). state float32 [slots, H, D, DV];
+    scratch: gates float32 >= ntok * (2 H + G), o float32 >= ntok * H * DV."""
+    _rows(cs, "cs", (_F32,)); _chk(ba, "ba", (_F32,)); _chk(out, "out", _SEQ_ACT); _chk(state, "state", (_F32,))
+    _chk(gates, "gates", (_F32,)); _chk(o, "o", (_F32,)); _chk(seg_starts, "seg_starts", (torch.int32,))
+    for t, n in ((A_log, "A_log"), (dt_bias, "dt_bias"), (norm_w, "norm_w")):
+        _chk(t, n, (_F32,))
+    ntok = cs.shape[0]
+    if gate is not None:
+        _rows(gate, "gate", (out.dtype,))
+    if cs.shape[1] < 2 * G * D + H * DV or ba.shape != (ntok, 2 * H) or out.shape != (ntok, H * DV) or state.shape[1:] != (H, D, DV) or \
+            gates.numel() < ntok * (2 * H + G) or o.numel() < ntok * H * DV or A_log.numel() != H or dt_bias.numel() != H or \
+            norm_w.numel() != DV or meta.shape != (5, ntok) or (gate is not None and gate.shape != (ntok, H * DV)):
+        raise ValueError("seq_delta_rule: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_delta_rule(cs.data_ptr(), cs.stride(0), _ptr(ba), _ptr(A_log), _ptr(dt_bias), _ptr(norm_w),
+                                              gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
+                                              _ptr(state), _ptr(gates), _ptr(o), _ptr(out), _ptr(meta), _ptr(seg_starts),
+                                              seg_starts.numel(), ntok, H, G, D, DV, float(unit_eps),
+                                              float(D ** -0.5 if q_mult is None else q_mult), float(eps), _sdt(out), _stream()),
+         "seq_delta_rule")
+
+
+def seq_selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, z: torch.Tensor,
+                       A_log: torch.Tensor, D_skip: torch.Tensor, state: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,
+                       seg_starts: torch.Tensor) -> None:
+    """Selective scan: dt = softplus(dt_pre + dt_bias) (float32 [ntok, inner]); per channel and state S <- exp(-dt exp(A_log)) S +
+    dt x B, y = S . C + D_skip x; out = y * silu(z). x, z, out [ntok, inner] and bc [ntok, 2 N] = [B | C] are views of the
+    activation type; state float32 [slots, inner, N]."""
+    _rows(x, "x", _SEQ_ACT)
+    for t, n in ((bc, "bc"), (z, "z"), (out, "out")):
+        _rows(t, n, (x.dtype,))
+    _rows(dt_pre, "dt_pre", (_F32,)); _chk(state, "state", (_F32,)); _chk(seg_starts, "seg_starts", (torch.int32,))
+    for t, n in ((dt_bias, "dt_bias"), (A_log, "A_log"), (D_skip, "D_skip")):
+        _chk(t, n, (_F32,))
+    ntok, inner = x.shape
+    N = A_log.shape[1]
+    if A_log.shape != (inner, N) or bc.shape != (ntok, 2 * N) or z.shape != (ntok, inner) or out.shape != (ntok, inner) or \
+            dt_pre.shape != (ntok, inner) or dt_bias.numel() != inner or D_skip.numel() != inner or state.shape[1:] != (inner, N) or \
+            meta.shape != (5, ntok):
+        raise ValueError("seq_selective_scan: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_selective_scan(x.data_ptr(), x.stride(0), dt_pre.data_ptr(), dt_pre.stride(0), _ptr(dt_bias),
+                                                  bc.data_ptr(), bc.stride(0), z.data_ptr(), z.stride(0), _ptr(A_log), _ptr(D_skip),
+                                                  _ptr(state), out.data_ptr(), out.stride(0), _ptr(meta), _ptr(seg_starts),
+                                                  seg_starts.numel(), ntok, inner, N, _sdt(x), _stream()), "seq_selective_scan")
+
+
+def seq_gqa_prep(p: torch.Tensor, qn_w: torch.Tensor, kn_w: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                 qout: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, meta: torch.Tensor, H: int, eps: float, *,
+                 v_norm: bool = True, v_first_in: Optional[torch.Tensor] = None, v_first_out: Optional[torch.Tensor] = None,
+                 mix: Optional[torch.Tensor] = None) -> None:
+    """Grouped-query attention after the fused projection p = [q (H x D) | k (G x D) | v (G x DV)] (biases added): per-head unit-RMS
+    norms with the weights qn_w / kn_w [D], rotation of the first rot_dims entries (entry i with i + rot_dims / 2, angle pos *
+    inv_freq[i]), values normed without a weight if v_norm, then v <- (1 - mix) v + mix v_first_in if v_first_in is given (mix a
+    float32 scalar tensor), else copied to v_first_out if that is given (both float32 [ntok, G * DV]). qout float32 [ntok, H, D];
+    cache_k [slots, cap, G, D], cache_v [slots, cap, G, DV] of p's type take row pos % cap."""
+    _rows(p, "p", _SEQ_ACT); _chk(qout, "qout", (_F32,)); _chk(cache_k, "cache_k", (p.dtype,)); _chk(cache_v, "cache_v", (p.dtype,))
+    _chk(qn_w, "qn_w", (_F32,)); _chk(kn_w, "kn_w", (_F32,)); _chk(inv_freq, "inv_freq", (_F32,), allow_none=rot_dims == 0)
+    _chk(v_first_in, "v_first_in", (_F32,), allow_none=True); _chk(v_first_out, "v_first_out", (_F32,), allow_none=True)
+    _chk(mix, "mix", (_F32,), allow_none=v_first_in is None)
+    ntok = p.shape[0]
+    slots, cap, G, D = cache_k.shape
+    DV = cache_v.shape[3]
+    if cache_v.shape[:3] != (slots, cap, G) or qout.shape != (ntok, H, D) or p.shape[1] < (H + G) * D + G * DV or qn_w.numel() != D or \
+            kn_w.numel() != D or meta.shape != (5, ntok) or (rot_dims and inv_freq.numel() != rot_dims // 2) or \
+            any(t is not None and t.numel() < ntok * G * DV for t in (v_first_in, v_first_out)):
+        raise ValueError("seq_gqa_prep: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_gqa_prep(p.data_ptr(), p.stride(0), _ptr(qn_w), _ptr(kn_w), _ptr(inv_freq), int(rot_dims),
+                                            _ptr(v_first_in), _ptr(v_first_out), _ptr(mix), _ptr(qout), _ptr(cache_k), _ptr(cache_v),
+                                            cap, _ptr(meta), ntok, H, G, D, DV, float(eps), int(v_norm), _sdt(p), _stream()),
+         "seq_gqa_prep")
+
+
+def seq_talking_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, talk: torch.Tensor, out: torch.Tensor,
+                          meta: torch.Tensor, window: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+    """Softmax attention whose heads' weights are mixed after the softmax: weight_g(j) = exp(s_g(j)) / (exp(sink[g]) + sum_j
+    exp(s_g(j))) with s = scale * q_g . k (sink None: no such term); head h applies sum_g talk[h, g] weight_g to the values of its
+    own key/value head. q float32 [ntok, H, D]; cache_k [slots, cap, G, D], cache_v [slots, cap, G, DV] (views with a unit last
+    stride, row = position % cap); talk float32 [H, H]; out [ntok, H, DV]; a token at position i sees keys j with 0 <= i - j <
+    window."""
+    import ctypes
+    _chk(q, "q", (_F32,)); _chk(out, "out", _SEQ_ACT); _chk(talk, "talk", (_F32,)); _chk(sink, "sink", (_F32,), allow_none=True)
+    if cache_k.dtype != out.dtype or cache_v.dtype != out.dtype or cache_k.stride(-1) != 1 or cache_v.stride(-1) != 1:
+        raise ValueError("seq_talking_attention: caches share out's element type and have a unit last stride")
+    ntok, H, D = q.shape
+    slots, cap, G, DK = cache_k.shape
+    DV = cache_v.shape[3]
+    if DK != D or out.shape != (ntok, H, DV) or cache_v.shape[:3] != (slots, cap, G) or talk.shape != (H, H) or meta.shape != (5, ntok) \
+            or (sink is not None and sink.numel() != H):
+        raise ValueError("seq_talking_attention: shapes do not match")
+    a = _lib.TalkingAttnArgs(q.data_ptr(), cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
+                             cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), _ptr(talk), _ptr(sink),
+                             _ptr(out), _ptr(meta), ntok, H, G, D, DV, int(window), cap, float(scale))
+    _seq(_lib.load_seq().qspec_seq_talking_attention(ctypes.byref(a), _sdt(out), _stream()), "seq_talking_attention")
+
+
+def seq_glu_clamp(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> None:
+    """out [ntok, F] = g * sigmoid(alpha g) * (u + 1) with g = min(gu[:, :F], limit), u = clamp(gu[:, F:], -limit, limit)."""
+    _chk(gu, "gu", _SEQ_ACT); _chk(out, "out", (gu.dtype,))
+    ntok, F = out.shape
+    if gu.shape != (ntok, 2 * F):
+        raise ValueError("seq_glu_clamp: gu must be [ntok, 2 F]")
+    _seq(_lib.load_seq().qspec_seq_glu_clamp(_ptr(gu), 2 * F, _ptr(out), ntok, F, float(limit), float(alpha), _sdt(gu), _stream()),
+         "seq_glu_clamp")
+
+
+def seq_scale(a: torch.Tensor, s: float) -> None:
+    """a <- s * a in place (float32)."""
+    _chk(a, "a", (_F32,))
+    _seq(_lib.load_seq().qspec_seq_scale_f32(_ptr(a), a.numel(), float(s), _stream()), "seq_scale")

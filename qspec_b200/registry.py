@@ -37,7 +37,7 @@ def architecture_of(cfg: dict) -> str:
 
 def supports_dtype(architecture: str, dtype: str) -> bool:
     dtype = _DTYPES.get(dtype, dtype)
-    if architecture in ("Mutusun", "Pitudra", "Repepel"):
+    if architecture in ("Mutusun", "Pitudra", "Repepel", "Kinanex"):
         return dtype in ("bfloat16", "float32")
     return dtype == "float16"          # the int4 decoders run float16 activations only
 
@@ -79,6 +79,16 @@ def _load_repepel(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: i
                                         max_seq_tokens=max_seq_tokens)
 
 
+def _load_kinanex(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 2048, max_seq_tokens=None, **_):
+    import torch
+    from .kinanex import KinanexModel
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32, None: torch.bfloat16}.get(dtype)
+    if dt is None:
+        raise ValueError(f"Kinanex runs in bfloat16 or float32, not {dtype}")
+    return KinanexModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens,
+                                        max_seq_tokens=max_seq_tokens)
+
+
 def _load_qspec_llama(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 256, **_):
     """The int4 dual-mode decoder (Llama-3 / Qwen2.5 shapes) from a Hugging Face style config.json; weights from the
     folder's QuaRot-format safetensors shards if there are any, random otherwise."""
@@ -103,5 +113,6 @@ def _load_qspec_llama(path, cfg, dtype, device, n_slots: int = 8, max_step_token
 register("Mutusun", _load_mutusun)
 register("Pitudra", _load_pitudra)
 register("Repepel", _load_repepel)
+register("Kinanex", _load_kinanex)
 register("LlamaForCausalLM", _load_qspec_llama)
 register("Qwen2ForCausalLM", _load_qspec_llama)
