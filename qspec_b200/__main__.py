@@ -30,7 +30,7 @@ def _generate(argv) -> int:
     from .build import build_library, build_seq_library
     arch = registry.architecture_of(registry.read_config(args.model))
     build_seq_library()
-    if arch not in ("Mutusun", "Pitudra", "Repepel"):
+    if arch not in registry.SEQUENCE_DESIGNS:
         build_library()
     from .scheduler import Scheduler
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt]

@@ -562,6 +562,11 @@ static int launch_mamba(const void* x, int x_ld, const float* dt_pre, int dt_ld,
   while (RG * NS < N) RG <<= 1;
   const int CH = 128 / RG, NP = RG * NS;
   const size_t smem = (size_t)(2 * BT * NP + 3 * BT * CH) * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(mamba_scan_kernel<T, NS, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
   launch_pdl(mamba_scan_kernel<T, NS, BT>, dim3(nseg, (inner + CH - 1) / CH), dim3(128), smem, st, (const T*)x, x_ld, dt_pre, dt_ld, dt_bias,
              (const T*)bc, bc_ld, (const T*)z, z_ld, A_log, Dp, state, (T*)out, out_ld, meta, seg_starts, ntok, inner, N, RG);
   QSPEC_CHECK_LAUNCH(1);

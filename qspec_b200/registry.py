@@ -11,6 +11,7 @@ import os
 from typing import Callable, Dict
 
 _LOADERS: Dict[str, Callable] = {}
+SEQUENCE_DESIGNS = ("Mutusun", "Pitudra", "Repepel", "Kinanex")      # served by the sequence-mixer library alone, bfloat16 / float32
 _DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32", "float16": "float16", "fp16": "float16"}
 
 
@@ -37,7 +38,7 @@ def architecture_of(cfg: dict) -> str:
 
 def supports_dtype(architecture: str, dtype: str) -> bool:
     dtype = _DTYPES.get(dtype, dtype)
-    if architecture in ("Mutusun", "Pitudra", "Repepel", "Kinanex"):
+    if architecture in SEQUENCE_DESIGNS:
         return dtype in ("bfloat16", "float32")
     return dtype == "float16"          # the int4 decoders run float16 activations only
 
