@@ -325,7 +325,7 @@ def write_safetensors_file(path: str, tensors: Mapping[str, torch.Tensor]) -> No
     header, blobs, at = {}, [], 0
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""     # reshape: a scalar has no last dimension to split
         header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
         blobs.append(raw)
         at += len(raw)

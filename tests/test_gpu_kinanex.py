@@ -330,7 +330,8 @@ def test_a_far_key_among_hundreds_is_found(dtype, decoded):
     ops.seq_talking_attention(dev(q[rows]), ck, cv, dev(talk), out, tab, n - 1 - far, 1.0, sink=sink)   # sees far + 1 .. only
     assert float(out[-1, 2].float().mean()) < 1.0
     ops.seq_talking_attention(dev(q[rows]), ck, cv, dev(talk), out, tab, n - far, 1.0, sink=sink)       # the key is the window's first
-    close(out[-1], want[n - 1], dtype, scale=float(want[rows].abs().max()))
+    inside = O.talking_attention(q[far:], k[far:], v[far:], talk, 1.0)                                    # the same keys, counted from the window's start
+    close(out[-1], inside[-1], dtype, scale=float(want[rows].abs().max()))
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
