@@ -44,12 +44,13 @@ def parse():
     ap.add_argument("--no-per-layer", action="store_true")
     ap.add_argument("--agree-shifts", default="19,20,18",
                     help="embedding shifts tried for the agree-by-construction (high-acceptance) point; '' disables it")
-    ap.add_argument("--design", default="qspec", choices=["qspec", "mutusun", "pitudra", "repepel"],
+    ap.add_argument("--design", default="qspec", choices=["qspec", "mutusun", "pitudra", "repepel", "kinanex"],
                     help="mutusun: prefill / decode throughput and kernel rooflines of the Mutusun design next to the int4 "
                          "decoder at equal sizes; pitudra: the same for the Pitudra design next to Mutusun "
                          "(qspec_b200/bench_seq.py); repepel: the same for the Repepel design next to Pitudra "
-                         "(qspec_b200/bench_repepel.py); the default workload is unchanged")
-    ap.add_argument("--sizes", default="", help="--design mutusun / pitudra / repepel: comma-separated size names (default: all)")
+                         "(qspec_b200/bench_repepel.py); kinanex: the same for the Kinanex design next to Pitudra "
+                         "(qspec_b200/bench_kinanex.py); the default workload is unchanged")
+    ap.add_argument("--sizes", default="", help="--design mutusun / pitudra / repepel / kinanex: comma-separated size names (default: all)")
     a = ap.parse_args()
     if a.seqs is None:
         a.seqs = 32 if a.model == "70b" else 64
@@ -130,9 +131,11 @@ def cpu_reference(args, seqs, budget_s, max_samples):
 
 def main():
     args = parse()
-    if args.design in ("mutusun", "pitudra", "repepel"):
+    if args.design in ("mutusun", "pitudra", "repepel", "kinanex"):
         from qspec_b200 import bench_seq
-        if args.design == "repepel":
+        if args.design == "kinanex":
+            from qspec_b200.bench_kinanex import run_kinanex as run
+        elif args.design == "repepel":
             from qspec_b200.bench_repepel import run_repepel as run
         else:
             run = bench_seq.run if args.design == "mutusun" else bench_seq.run_pitudra
