@@ -313,7 +313,8 @@ int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, const float* kn
  * weight_g(j) = exp(s_g(j)) / (exp(sink[g]) + sum_j exp(s_g(j))), s = scale * q_g . key of g's key/value head (sink NULL: no such
  * term); head h applies sum_g talk[h, g] weight_g(j) to the values of its own key/value head h / (H / G). q float32 [ntok, H, D];
  * keys and values as rows of per-slot rings with element strides, as for qspec_seq_window_attention; talk float32 [H, H];
- * out [ntok, H, DV]. H * DV <= 16384. */
+ * out [ntok, H, DV]. rows_per_cta: 4 lets a CTA take four consecutive batch rows, which share every key and value row they
+ * read when they belong to one sequence (prompt portions); 1 gives every row a CTA of its own (decode-shaped batches). */
 typedef struct qspec_talking_attn_args {
   const float* q;
   const void* k; long long k_slot_stride; int k_row_stride, k_head_stride;
@@ -321,7 +322,7 @@ typedef struct qspec_talking_attn_args {
   const float* talk; const float* sink;
   void* out; const int* meta; int ntok, H, G, D, DV, window, cap; float scale;
 } qspec_talking_attn_args;
-int qspec_seq_talking_attention(const qspec_talking_attn_args* args, int dtype, void* stream);
+int qspec_seq_talking_attention(const qspec_talking_attn_args* args, int rows_per_cta, int dtype, void* stream);
 
 /* out[t, f] = g * sigmoid(alpha g) * (u + 1), g = min(gu[t, f], limit), u = clamp(gu[t, F + f], -limit, limit): rows of gu are
  * [gate (F) | up (F)] with leading dimension ld; out [ntok, F]. */

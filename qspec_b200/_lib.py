@@ -177,7 +177,7 @@ SEQ_SIGNATURES = {
     "qspec_seq_gqa_prep": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                    c_void_p]),
-    "qspec_seq_talking_attention": (c_int, [c_void_p, c_int, c_void_p]),
+    "qspec_seq_talking_attention": (c_int, [c_void_p, c_int, c_int, c_void_p]),
     "qspec_seq_glu_clamp": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "qspec_seq_scale_f32": (c_int, [c_void_p, c_ll, c_float, c_void_p]),
 }

@@ -5,6 +5,7 @@
 #include "seq_common.cuh"
 #include "../../include/qspec_b200_seq.h"
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace qspec {
 
@@ -103,9 +104,11 @@ delta_scan_kernel(const float* __restrict__ cs, int ld, const float* __restrict_
                   float* __restrict__ o, const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int H, int G,
                   int D, int DV) {
   pdl_enter();
-  constexpr int DP = 8 * NS;
+  // a row group's NS values sit SP apart, so that the eight groups' 16-byte reads fall on different banks
+  constexpr int SP = NS >= 8 ? NS + 4 : NS, DP = 8 * SP;
   __shared__ __align__(16) float sk[2][BT][DP], sq[2][BT][DP];
-  __shared__ float sv[2][BT][16], sg[2][BT][4];                  // gates: beta, decay, q.k
+  __shared__ float sv[2][BT][16];
+  __shared__ __align__(16) float sg[2][BT][4];                   // gates: beta, decay, q.k
   const int i = seg_starts[blockIdx.x], h = blockIdx.y, v0 = blockIdx.z * 16;
   const TokMeta mt = load_meta(meta, ntok, i);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -124,8 +127,9 @@ delta_scan_kernel(const float* __restrict__ cs, int ld, const float* __restrict_
     for (int e = tid; e < nb * D; e += 128) {
       const int tt = e / D, d = e - tt * D;
       const float* src = cs + (size_t)(tb + tt) * ld + (size_t)kq * D + d;
-      cp_async_4(&sq[buf][tt][d], src);
-      cp_async_4(&sk[buf][tt][d], src + GD);
+      const int at = (d / NS) * SP + d % NS;
+      cp_async_4(&sq[buf][tt][at], src);
+      cp_async_4(&sk[buf][tt][at], src + GD);
     }
     for (int e = tid; e < nb * 16; e += 128) {
       const int tt = e >> 4, c = e & 15;
@@ -145,9 +149,9 @@ delta_scan_kernel(const float* __restrict__ cs, int ld, const float* __restrict_
     __syncthreads();
     const int nb = min(BT, mt.seg_end - tb);
     for (int tt = 0; tt < nb; ++tt) {
-      const float4* k4 = reinterpret_cast<const float4*>(&sk[buf][tt][d0]);
-      const float4* q4 = reinterpret_cast<const float4*>(&sq[buf][tt][d0]);
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+      const float4* k4 = reinterpret_cast<const float4*>(&sk[buf][tt][rg * SP]);
+      const float4* q4 = reinterpret_cast<const float4*>(&sq[buf][tt][rg * SP]);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;   // short chains: the sums are on the token's critical path
       float kr[NS];
 #pragma unroll
       for (int r = 0; r < NS / 4; ++r) {
@@ -155,16 +159,17 @@ delta_scan_kernel(const float* __restrict__ cs, int ld, const float* __restrict_
         kr[4 * r] = k.x; kr[4 * r + 1] = k.y; kr[4 * r + 2] = k.z; kr[4 * r + 3] = k.w;
         a0 += S[4 * r] * k.x;     b0 += S[4 * r] * q.x;
         a1 += S[4 * r + 1] * k.y; b1 += S[4 * r + 1] * q.y;
-        a0 += S[4 * r + 2] * k.z; b0 += S[4 * r + 2] * q.z;
-        a1 += S[4 * r + 3] * k.w; b1 += S[4 * r + 3] * q.w;
+        a2 += S[4 * r + 2] * k.z; b2 += S[4 * r + 2] * q.z;
+        a3 += S[4 * r + 3] * k.w; b3 += S[4 * r + 3] * q.w;
       }
-      float a = a0 + a1, b = b0 + b1;
+      float a = (a0 + a1) + (a2 + a3), b = (b0 + b1) + (b2 + b3);
 #pragma unroll
       for (int off = 1; off < 8; off <<= 1) {
         a += __shfl_xor_sync(0xffffffffu, a, off);
         b += __shfl_xor_sync(0xffffffffu, b, off);
       }
-      const float beta = sg[buf][tt][0], g = sg[buf][tt][1], qk = sg[buf][tt][2];
+      const float4 gt = *reinterpret_cast<const float4*>(&sg[buf][tt][0]);
+      const float beta = gt.x, g = gt.y, qk = gt.z;
       const float v = live ? sv[buf][tt][cc] : 0.f;
       const float u = beta * (v - g * a);
 #pragma unroll
@@ -206,22 +211,20 @@ head_norm_gate_kernel(const float* __restrict__ src, const float* __restrict__ w
 // Per channel c and state n: S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c;
 // out = y * silu(z). dt = softplus(dt_pre + dt_bias), A = -exp(A_log). RG neighbouring lanes share a channel, each with NS
 // states in registers; their partial read-outs are added by shuffles, which is not part of the chain from token to token. One
-// CTA of 128 threads per (segment, 128 / RG channels) walks the segment in blocks of BT tokens whose B, C, x and dt it first
-// copies to shared memory (dt after the softplus); outputs are written per block.
-template <typename T, int NS, int BT>
+// CTA of 128 threads per (segment, 128 / RG channels) walks the segment in blocks of BT tokens. A block's B, C, x, dt and z
+// are fetched into registers while the block before it is applied, then parked in shared memory (dt after the softplus);
+// outputs are written per block.
+template <typename T, int NS, int RG>
 __global__ void __launch_bounds__(128)
 mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ dt_pre, int dt_ld, const float* __restrict__ dt_bias,
                   const T* __restrict__ bc, int bc_ld, const T* __restrict__ z, int z_ld, const float* __restrict__ A_log,
                   const float* __restrict__ Dp, float* __restrict__ state, T* __restrict__ out, int out_ld,
-                  const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int inner, int N, int RG) {
+                  const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int inner, int N) {
   pdl_enter();
-  extern __shared__ __align__(16) float sm_ms[];                 // B [BT][NP] | C [BT][NP] | x [BT][CH] | dt [BT][CH] | y [BT][CH]
-  const int CH = 128 / RG, NP = RG * NS;
-  float* sB = sm_ms;
-  float* sC = sB + BT * NP;
-  float* sx = sC + BT * NP;
-  float* sdt = sx + BT * CH;
-  float* sy = sdt + BT * CH;
+  constexpr int CH = 128 / RG, NP = RG * NS, BT = RG >= 8 ? 2 : 16 / RG;
+  constexpr int XR = (BT * CH + 127) / 128, BR = (BT * NP + 127) / 128;
+  __shared__ __align__(16) float sB[BT][NP], sC[BT][NP];
+  __shared__ float sx[BT][CH], sdt[BT][CH], sz[BT][CH], sy[BT][CH];
   const int i = seg_starts[blockIdx.x];
   const TokMeta mt = load_meta(meta, ntok, i);
   const int tid = threadIdx.x, rg = tid % RG, lc = tid / RG, c0 = blockIdx.y * CH, c = c0 + lc;
@@ -235,29 +238,51 @@ mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ d
     A[r] = ok ? -expf(A_log[(size_t)c * N + n0 + r]) : 0.f;
     S[r] = (ok && mt.pos > 0) ? st[n0 + r] : 0.f;
   }
+  float rx[XR], rd[XR], rz[XR], rb[BR], rc[BR];
+  // every load of a block is issued before the first one is used: addresses outside the block are clamped into it rather than
+  // skipped (a branch around a load would make the loads wait for one another), and what they bring is never used
+  auto fetch = [&](int tb) {
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int e = min(tid + 128 * r, BT * CH - 1), tt = e / CH, k = e % CH;
+      const int t = min(tb + tt, mt.seg_end - 1), ch = min(c0 + k, inner - 1);
+      rx[r] = to_f(x[(size_t)t * x_ld + ch]);
+      rd[r] = dt_pre[(size_t)t * dt_ld + ch] + dt_bias[ch];
+      rz[r] = to_f(z[(size_t)t * z_ld + ch]);
+    }
+#pragma unroll
+    for (int r = 0; r < BR; ++r) {
+      const int e = min(tid + 128 * r, BT * NP - 1), tt = e / NP, n = e % NP;
+      const int t = min(tb + tt, mt.seg_end - 1), ns = min(n, N - 1);
+      const T* row = bc + (size_t)t * bc_ld;
+      const float b = to_f(row[ns]), cc = to_f(row[N + ns]);
+      rb[r] = n < N ? b : 0.f;
+      rc[r] = n < N ? cc : 0.f;
+    }
+  };
+  fetch(mt.seg_begin);
   for (int tb = mt.seg_begin; tb < mt.seg_end; tb += BT) {
     const int nb = min(BT, mt.seg_end - tb);
-    for (int e = tid; e < nb * NP; e += 128) {
-      const int tt = e / NP, n = e - tt * NP;
-      const T* row = bc + (size_t)(tb + tt) * bc_ld;
-      sB[tt * NP + n] = n < N ? to_f(row[n]) : 0.f;
-      sC[tt * NP + n] = n < N ? to_f(row[N + n]) : 0.f;
-    }
-    for (int e = tid; e < nb * CH; e += 128) {
-      const int tt = e / CH, k = e - tt * CH, ch = c0 + k;
-      float xv = 0.f, dv = 0.f;
-      if (ch < inner) {
-        xv = to_f(x[(size_t)(tb + tt) * x_ld + ch]);
-        dv = softplus_f(dt_pre[(size_t)(tb + tt) * dt_ld + ch] + dt_bias[ch]);
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int e = tid + 128 * r;
+      if (e < BT * CH) {
+        (&sx[0][0])[e] = rx[r];
+        (&sdt[0][0])[e] = softplus_f(rd[r]);
+        (&sz[0][0])[e] = rz[r];
       }
-      sx[tt * CH + k] = xv;
-      sdt[tt * CH + k] = dv;
+    }
+#pragma unroll
+    for (int r = 0; r < BR; ++r) {
+      const int e = tid + 128 * r;
+      if (e < BT * NP) { (&sB[0][0])[e] = rb[r]; (&sC[0][0])[e] = rc[r]; }
     }
     __syncthreads();
+    if (tb + BT < mt.seg_end) fetch(tb + BT);
     for (int tt = 0; tt < nb; ++tt) {
-      const float dt = sdt[tt * CH + lc], dx = dt * sx[tt * CH + lc];
-      const float4* B4 = reinterpret_cast<const float4*>(sB + tt * NP + n0);
-      const float4* C4 = reinterpret_cast<const float4*>(sC + tt * NP + n0);
+      const float dt = sdt[tt][lc], dx = dt * sx[tt][lc];
+      const float4* B4 = reinterpret_cast<const float4*>(&sB[tt][n0]);
+      const float4* C4 = reinterpret_cast<const float4*>(&sC[tt][n0]);
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int r = 0; r < NS / 4; ++r) {
@@ -268,16 +293,15 @@ mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ d
         S[4 * r + 3] = expf(dt * A[4 * r + 3]) * S[4 * r + 3] + dx * b.w; y1 += S[4 * r + 3] * cq.w;
       }
       float y = y0 + y1;
+#pragma unroll
       for (int off = 1; off < RG; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
-      if (rg == 0) sy[tt * CH + lc] = y;
+      if (rg == 0) sy[tt][lc] = y;
     }
     __syncthreads();
     for (int e = tid; e < nb * CH; e += 128) {
-      const int tt = e / CH, k = e - tt * CH, ch = c0 + k;
-      if (ch < inner) {
-        const float zz = to_f(z[(size_t)(tb + tt) * z_ld + ch]);
-        out[(size_t)(tb + tt) * out_ld + ch] = from_f<T>((sy[tt * CH + k] + Dp[ch] * sx[tt * CH + k]) * silu_f(zz));
-      }
+      const int tt = e / CH, k = e % CH, ch = c0 + k;
+      if (ch < inner)
+        out[(size_t)(tb + tt) * out_ld + ch] = from_f<T>((sy[tt][k] + Dp[ch] * sx[tt][k]) * silu_f(sz[tt][k]));
     }
     __syncthreads();
   }
@@ -353,112 +377,286 @@ gqa_prep_kernel(const T* __restrict__ p, int ld, const float* __restrict__ qn_w,
 
 // ---- softmax attention whose heads' weights are mixed after the softmax ("talking heads") ------------------------------------
 // weight_g(j) = exp(s_g(j)) / (exp(sink_g) + sum_j exp(s_g(j))) for every query head g of a token; then head h uses
-// sum_g talk[h, g] weight_g(j) on the values of ITS key/value head. Because the mix needs finished weights of all heads, a token
-// is one CTA that makes two passes over its keys: the first finds every head's maximum and denominator, the second recomputes
-// the scores of a block of BK keys, turns them into weights, mixes them through shared memory and applies them to the values.
-// A warp takes the key rows of a block in turn (lanes along the row, the row's elements stay in registers for all query heads
-// of the group). Which thread takes which key or output depends on nothing but the sizes, so a token's result does not depend
-// on its neighbours in the batch or on how its sequence was cut.
-template <typename T, int NACC, int BK>
+// sum_g talk[h, g] weight_g(j) on the values of ITS key/value head. Because the mix needs finished weights of all heads, a CTA
+// holds all heads of its tokens and makes two passes over the keys: the first finds every head's maximum and denominator, the
+// second recomputes the scores of a block of BK keys, turns them into weights, mixes them through shared memory and applies
+// them to the values. A CTA takes NQ consecutive batch rows; rows of one sequence share every key and value row that is read
+// (prompt portions: NQ = 4), rows of different sequences are taken one after the other (decode-shaped batches launch NQ = 1).
+//   scores   thread = (key of the block, key/value head): the key row passes through registers in 16-byte pieces and meets the
+//            queries of all heads of its group and all NQ tokens (queries wait in shared memory, pre-multiplied by the scale)
+//   mix      thread = (token, key, four heads): talk is kept transposed so that four heads' factors are one load
+//   values   thread = (key/value head, two value columns): one value load serves the heads of the group and the NQ tokens; the
+//            accumulators live in shared memory between blocks
+// The block partition of the keys starts at the first key the group's first row sees, so with a full-length window every token's
+// sums run in the same order however its sequence was cut. nsplit > 1 (NQ = 1 only): the CTAs of a cluster (grid y) take a
+// token's key blocks in turn; they exchange their maxima and denominators after the first pass and add their partial outputs
+// after the second through distributed shared memory, in rank order.
+template <typename T, int REP, int NQ>
 __global__ void __launch_bounds__(256)
 talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long long k_ss, int k_rs, int k_hs,
                     const T* __restrict__ vc, long long v_ss, int v_rs, int v_hs, const float* __restrict__ talk,
                     const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G, int D,
-                    int DV, int window, int cap, float scale) {
+                    int DV, int window, int cap, float scale, int vec_k, int vec_v, int nsplit) {
   pdl_enter();
-  extern __shared__ float sm_ta[];                                // q [H][D] | talk [H][H] | S [H][BK] | Wm [H][BK] | m [H] | rl [H]
-  const int i = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  float* sq = sm_ta;
-  float* stalk = sq + H * D;
-  float* sS = stalk + H * H;
-  float* sW = sS + H * BK;
-  float* sm = sW + H * BK;
-  float* srl = sm + H;
-  const int slot = meta[i], pos = meta[ntok + i];
-  const int rep = H / G;
-  for (int e = tid; e < H * D; e += 256) sq[e] = q[(size_t)i * H * D + e] * scale;
-  for (int e = tid; e < H * H; e += 256) stalk[e] = talk[e];
-  for (int g = tid; g < H; g += 256) { sm[g] = sink ? sink[g] : -INFINITY; srl[g] = sink ? 1.f : 0.f; }
-  __syncthreads();
-  const T* kbase = kc + (size_t)slot * k_ss;
-  const T* vbase = vc + (size_t)slot * v_ss;
-  const int j0 = max(0, pos - window + 1);
-  float acc[NACC];
-#pragma unroll
-  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
-
-  // scores of the keys jb .. jb + BK - 1 for all heads into sS (keys beyond pos: -inf)
-  auto scores = [&](int jb) {
-    for (int e = warp; e < BK * G; e += 8) {
-      const int jj = e / G, kg = e - jj * G, j = jb + jj;
-      if (j > pos) {
-        for (int r = lane; r < rep; r += 32) sS[(kg * rep + r) * BK + jj] = -INFINITY;
-        continue;
-      }
-      const T* kr = kbase + (size_t)(j % cap) * k_rs + (size_t)kg * k_hs;
-      for (int r = 0; r < rep; ++r) {
-        const float* qh = sq + (size_t)(kg * rep + r) * D;
-        float dot = 0.f;
-        for (int c = lane; c < D; c += 32) dot += qh[c] * to_f(kr[c]);
-        dot = warp_xor_sum(dot);
-        if (lane == 0) sS[(kg * rep + r) * BK + jj] = dot;
-      }
-    }
-  };
-
-  // pass 1: maxima and denominators
-  for (int jb = j0; jb <= pos; jb += BK) {
-    scores(jb);
-    __syncthreads();
-    for (int g = tid; g < H; g += 256) {
-      float m = sm[g], l = srl[g];
-      float mn = m;
-      for (int jj = 0; jj < BK; ++jj) mn = fmaxf(mn, sS[g * BK + jj]);
-      if (mn > -INFINITY) {
-        l *= expf(m - mn);
-        for (int jj = 0; jj < BK; ++jj) l += expf(sS[g * BK + jj] - mn);
-      }
-      sm[g] = mn; srl[g] = l;
-    }
-    __syncthreads();
+  constexpr int BK = 64, KV = 16 / (int)sizeof(T);                // keys per block; elements of a 16-byte piece
+  extern __shared__ __align__(16) float sm_ta[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int HP = (H + 3) & ~3, DP = (D + 3) & ~3, rep = H / G;
+  float* sq = sm_ta;                                              // [NQ][H][DP]
+  float* stalk = sq + NQ * H * DP;                                // [H][HP]: stalk[g][h] = talk[h][g]
+  float* sS = stalk + H * HP;                                     // [NQ][H][BK]
+  float* sW = sS + NQ * H * BK;                                   // [NQ][H][BK]
+  float* sO = sW + NQ * H * BK;                                   // [NQ][H][DV]
+  float* smx = sO + NQ * H * DV;                                  // [NQ][H] maxima
+  float* srl = smx + NQ * H;                                      // [NQ][H] denominators, then their reciprocals
+  float* spm = srl + NQ * H;                                      // [NQ][H] this CTA's own maxima / denominators, read by its cluster
+  float* spl = spm + NQ * H;
+  const int rank = blockIdx.y;
+  for (int e = tid; e < H * HP; e += 256) {
+    const int g = e / HP, h = e - g * HP;
+    stalk[e] = h < H ? talk[h * H + g] : 0.f;
   }
-  for (int g = tid; g < H; g += 256) srl[g] = srl[g] > 0.f ? 1.0f / srl[g] : 0.f;
-  __syncthreads();
-  // pass 2: weights, mix, values
-  for (int jb = j0; jb <= pos; jb += BK) {
-    scores(jb);
-    __syncthreads();
-    for (int e = tid; e < H * BK; e += 256) {
-      const int g = e / BK;
-      sS[e] = expf(sS[e] - sm[g]) * srl[g];                       // exp(-inf) = 0 for keys beyond the token
+  const int row0 = blockIdx.x * NQ, rows_end = min(row0 + NQ, ntok);
+  const int CP = (DV + 1) / 2, RC = (rep + REP - 1) / REP;
+  int first = row0;
+  while (first < rows_end) {
+    // the rows first .. first + nq - 1 belong to one sequence (consecutive positions)
+    const int slot = meta[first], pos0 = meta[ntok + first], seg_end = meta[3 * ntok + first];
+    const int nq = min(rows_end, seg_end) - first;
+    const int posl = pos0 + nq - 1;
+    const int j0 = max(0, pos0 - window + 1);
+    __syncthreads();                                             // the previous group is done with the shared buffers
+    for (int e = tid; e < nq * H * DP; e += 256) {
+      const int r = e / DP, c = e - r * DP;
+      sq[e] = c < D ? q[((size_t)first * H + r) * D + c] * scale : 0.f;
     }
-    __syncthreads();
-    for (int e = tid; e < H * BK; e += 256) {
-      const int h = e / BK, jj = e - h * BK;
-      float s = 0.f;
-      for (int g = 0; g < H; ++g) s += stalk[h * H + g] * sS[g * BK + jj];
-      sW[e] = s;
+    for (int e = tid; e < nq * H; e += 256) {                    // the sink's term is counted once: by rank 0
+      const bool sk = sink && rank == 0;
+      smx[e] = sk ? sink[e % H] : -INFINITY;
+      srl[e] = sk ? 1.f : 0.f;
     }
+    for (int e = tid; e < nq * H * DV; e += 256) sO[e] = 0.f;
     __syncthreads();
-    const int nk = min(BK, pos - jb + 1);
+    const T* kbase = kc + (size_t)slot * k_ss;
+    const T* vbase = vc + (size_t)slot * v_ss;
+
+    auto scores = [&](int jb) {
+      for (int e = tid; e < BK * G; e += 256) {
+        const int kg = e / BK, jj = e - kg * BK, j = jb + jj;
+        float d[NQ][REP];
 #pragma unroll
-    for (int a = 0; a < NACC; ++a) {
-      const int e = tid + 256 * a;
-      if (e < H * DV) {
-        const int h = e / DV, c = e - h * DV;
-        const T* vcol = vbase + (size_t)(h / rep) * v_hs + c;
-        const float* wr = sW + h * BK;
-        float s = acc[a];
-        for (int jj = 0; jj < nk; ++jj) s += wr[jj] * to_f(vcol[(size_t)((jb + jj) % cap) * v_rs]);
-        acc[a] = s;
+        for (int a = 0; a < NQ; ++a)
+#pragma unroll
+          for (int r = 0; r < REP; ++r) d[a][r] = 0.f;
+        for (int rc = 0; rc < RC; ++rc) {
+          const int h0 = kg * rep + rc * REP, nr = min(REP, rep - rc * REP);
+          if (j <= posl) {
+            const T* kr = kbase + (size_t)(j % cap) * k_rs + (size_t)kg * k_hs;
+            if (vec_k) {
+              // 16-byte pieces of the key row, eight (then two, then one) in flight before the first is used
+              auto piece = [&](const uint4& u, int c) {
+                float kf[8];
+                if (sizeof(T) == 2) {
+                  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                  const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.z));
+                  const float2 a3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.w));
+                  kf[0] = a0.x; kf[1] = a0.y; kf[2] = a1.x; kf[3] = a1.y; kf[4] = a2.x; kf[5] = a2.y; kf[6] = a3.x; kf[7] = a3.y;
+                } else {
+                  kf[0] = __uint_as_float(u.x); kf[1] = __uint_as_float(u.y); kf[2] = __uint_as_float(u.z); kf[3] = __uint_as_float(u.w);
+                  kf[4] = kf[5] = kf[6] = kf[7] = 0.f;
+                }
+#pragma unroll
+                for (int a = 0; a < NQ; ++a)
+#pragma unroll
+                  for (int r = 0; r < REP; ++r)
+                    if (a < nq && r < nr) {
+                      const float4* q4 = reinterpret_cast<const float4*>(sq + (size_t)(a * H + h0 + r) * DP + c);
+#pragma unroll
+                      for (int x = 0; x < KV / 4; ++x) {
+                        const float4 qq = q4[x];
+                        d[a][r] += qq.x * kf[4 * x] + qq.y * kf[4 * x + 1] + qq.z * kf[4 * x + 2] + qq.w * kf[4 * x + 3];
+                      }
+                    }
+              };
+              const uint4* k16 = reinterpret_cast<const uint4*>(kr);
+              const int np = D / KV;
+              int pc = 0;
+              for (; pc + 8 <= np; pc += 8) {
+                uint4 u[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) u[x] = k16[pc + x];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) piece(u[x], (pc + x) * KV);
+              }
+              for (; pc + 2 <= np; pc += 2) {
+                const uint4 u0 = k16[pc], u1 = k16[pc + 1];
+                piece(u0, pc * KV);
+                piece(u1, (pc + 1) * KV);
+              }
+              if (pc < np) piece(k16[pc], pc * KV);
+            } else {
+              for (int c = 0; c < D; ++c) {
+                const float kv = to_f(kr[c]);
+#pragma unroll
+                for (int a = 0; a < NQ; ++a)
+#pragma unroll
+                  for (int r = 0; r < REP; ++r)
+                    if (a < nq && r < nr) d[a][r] += sq[(size_t)(a * H + h0 + r) * DP + c] * kv;
+              }
+            }
+          }
+#pragma unroll
+          for (int a = 0; a < NQ; ++a)
+#pragma unroll
+            for (int r = 0; r < REP; ++r)
+              if (a < nq && r < nr) {
+                const int pa = pos0 + a;
+                sS[(a * H + h0 + r) * BK + jj] = (j <= pa && pa - j < window) ? d[a][r] : -INFINITY;
+                d[a][r] = 0.f;
+              }
+        }
       }
+    };
+
+    // pass 1: maxima and denominators, one warp per (token, head) row in turn
+    for (int jb = j0 + rank * BK; jb <= posl; jb += nsplit * BK) {
+      scores(jb);
+      __syncthreads();
+      for (int r = warp; r < nq * H; r += 8) {
+        const float s0 = sS[r * BK + lane], s1 = sS[r * BK + 32 + lane];
+        const float m = smx[r];
+        const float mn = fmaxf(m, warp_xor_max(fmaxf(s0, s1)));
+        if (mn > -INFINITY) {                                     // uniform over the warp
+          const float part = warp_xor_sum(expf(s0 - mn) + expf(s1 - mn));
+          if (lane == 0) { srl[r] = srl[r] * expf(m - mn) + part; smx[r] = mn; }
+        }
+      }
+      __syncthreads();
     }
+    if (nsplit > 1) {                                            // every CTA of the cluster combines all the partial pairs, in rank order
+      for (int e = tid; e < nq * H; e += 256) { spm[e] = smx[e]; spl[e] = srl[e]; }
+      cluster_sync_all();
+      const uint32_t pm = (uint32_t)__cvta_generic_to_shared(spm), pl = (uint32_t)__cvta_generic_to_shared(spl);
+      for (int e = tid; e < nq * H; e += 256) {
+        float M = -INFINITY;
+        for (int r = 0; r < nsplit; ++r) M = fmaxf(M, __uint_as_float(ld_dsmem_u32(mapa_shared(pm + 4u * e, (uint32_t)r))));
+        float L = 0.f;
+        for (int r = 0; r < nsplit; ++r) {
+          const float m = __uint_as_float(ld_dsmem_u32(mapa_shared(pm + 4u * e, (uint32_t)r)));
+          const float l = __uint_as_float(ld_dsmem_u32(mapa_shared(pl + 4u * e, (uint32_t)r)));
+          if (m > -INFINITY) L += l * expf(m - M);
+        }
+        smx[e] = M; srl[e] = L;
+      }
+      __syncthreads();
+    }
+    for (int e = tid; e < nq * H; e += 256) srl[e] = srl[e] > 0.f ? 1.0f / srl[e] : 0.f;
     __syncthreads();
-  }
+    // pass 2: weights, mix, values
+    for (int jb = j0 + rank * BK; jb <= posl; jb += nsplit * BK) {
+      scores(jb);
+      __syncthreads();
+      for (int e = tid; e < nq * H * BK; e += 256) {
+        const int r = e / BK;
+        sS[e] = expf(sS[e] - smx[r]) * srl[r];                    // exp(-inf) = 0 for keys a row does not see
+      }
+      __syncthreads();
+      for (int e = tid; e < nq * (HP / 4) * BK; e += 256) {
+        const int jj = e % BK, t = e / BK, hc = t % (HP / 4), a = t / (HP / 4);
+        float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int g = 0; g < H; ++g) {
+          const float p = sS[(a * H + g) * BK + jj];
+          const float4 tk = *reinterpret_cast<const float4*>(stalk + g * HP + 4 * hc);
+          w.x += tk.x * p; w.y += tk.y * p; w.z += tk.z * p; w.w += tk.w * p;
+        }
+        const int h = 4 * hc;
+        sW[(a * H + h) * BK + jj] = w.x;
+        if (h + 1 < H) sW[(a * H + h + 1) * BK + jj] = w.y;
+        if (h + 2 < H) sW[(a * H + h + 2) * BK + jj] = w.z;
+        if (h + 3 < H) sW[(a * H + h + 3) * BK + jj] = w.w;
+      }
+      __syncthreads();
+      const int nk = min(BK, posl - jb + 1);
+      for (int e = tid; e < G * RC * CP; e += 256) {
+        const int cp = e % CP, t = e / CP, rc = t % RC, kg = t / RC;
+        const int c = 2 * cp, h0 = kg * rep + rc * REP, nr = min(REP, rep - rc * REP);
+        const bool two = c + 1 < DV;
+        float acc[NQ][REP][2];
 #pragma unroll
-  for (int a = 0; a < NACC; ++a) {
-    const int e = tid + 256 * a;
-    if (e < H * DV) out[(size_t)i * H * DV + e] = from_f<T>(acc[a]);
+        for (int a = 0; a < NQ; ++a)
+#pragma unroll
+          for (int r = 0; r < REP; ++r) {
+            const bool ok = a < nq && r < nr;
+            acc[a][r][0] = ok ? sO[(a * H + h0 + r) * DV + c] : 0.f;
+            acc[a][r][1] = ok && two ? sO[(a * H + h0 + r) * DV + c + 1] : 0.f;
+          }
+        const T* vcol = vbase + (size_t)kg * v_hs + c;
+        int jj = 0;
+        if (vec_v && two) {
+          // eight value rows in flight before the first is used; the weights of four keys are one 16-byte read
+          for (; jj + 8 <= nk; jj += 8) {
+            float2 vv[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              const int j = jb + jj + x;
+              const T* vp = vcol + (size_t)(j < cap ? j : j % cap) * v_rs;
+              if (sizeof(T) == 2) vv[x] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vp));
+              else vv[x] = *reinterpret_cast<const float2*>(vp);
+            }
+#pragma unroll
+            for (int a = 0; a < NQ; ++a)
+#pragma unroll
+              for (int r = 0; r < REP; ++r)
+                if (a < nq && r < nr) {
+                  const float4* w4 = reinterpret_cast<const float4*>(sW + (a * H + h0 + r) * BK + jj);
+                  const float4 wa = w4[0], wb = w4[1];
+                  acc[a][r][0] += wa.x * vv[0].x + wa.y * vv[1].x + wa.z * vv[2].x + wa.w * vv[3].x +
+                                  wb.x * vv[4].x + wb.y * vv[5].x + wb.z * vv[6].x + wb.w * vv[7].x;
+                  acc[a][r][1] += wa.x * vv[0].y + wa.y * vv[1].y + wa.z * vv[2].y + wa.w * vv[3].y +
+                                  wb.x * vv[4].y + wb.y * vv[5].y + wb.z * vv[6].y + wb.w * vv[7].y;
+                }
+          }
+        }
+        for (; jj < nk; ++jj) {
+          const int j = jb + jj;
+          const T* vp = vcol + (size_t)(j < cap ? j : j % cap) * v_rs;
+          const float v0 = to_f(vp[0]), v1 = two ? to_f(vp[1]) : 0.f;
+#pragma unroll
+          for (int a = 0; a < NQ; ++a)
+#pragma unroll
+            for (int r = 0; r < REP; ++r)
+              if (a < nq && r < nr) {
+                const float w = sW[(a * H + h0 + r) * BK + jj];
+                acc[a][r][0] += w * v0;
+                acc[a][r][1] += w * v1;
+              }
+        }
+#pragma unroll
+        for (int a = 0; a < NQ; ++a)
+#pragma unroll
+          for (int r = 0; r < REP; ++r)
+            if (a < nq && r < nr) {
+              sO[(a * H + h0 + r) * DV + c] = acc[a][r][0];
+              if (two) sO[(a * H + h0 + r) * DV + c + 1] = acc[a][r][1];
+            }
+      }
+      __syncthreads();
+    }
+    if (nsplit > 1) {                                            // CTA r adds slice r of the outputs over the ranks, in rank order
+      cluster_sync_all();
+      const int n = nq * H * DV, per = (n + nsplit - 1) / nsplit, e_end = min(n, (rank + 1) * per);
+      const uint32_t po = (uint32_t)__cvta_generic_to_shared(sO);
+      for (int e = rank * per + tid; e < e_end; e += 256) {
+        float v = 0.f;
+        for (int r = 0; r < nsplit; ++r) v += __uint_as_float(ld_dsmem_u32(mapa_shared(po + 4u * e, (uint32_t)r)));
+        out[(size_t)first * H * DV + e] = from_f<T>(v);
+      }
+      cluster_sync_all();                                        // nobody leaves while its partial sums may still be read
+    } else {
+      for (int e = tid; e < nq * H * DV; e += 256) out[(size_t)first * H * DV + e] = from_f<T>(sO[e]);
+    }
+    first += nq;
   }
 }
 
@@ -553,24 +751,32 @@ extern "C" int qspec_seq_delta_rule(float* cs, int ld, const float* ba, const fl
   return QSPEC_OK;
 }
 
-template <typename T, int NS>
+template <typename T, int NS, int RG>
 static int launch_mamba(const void* x, int x_ld, const float* dt_pre, int dt_ld, const float* dt_bias, const void* bc, int bc_ld, const void* z,
                         int z_ld, const float* A_log, const float* Dp, float* state, void* out, int out_ld, const int* meta,
                         const int* seg_starts, int nseg, int ntok, int inner, int N, cudaStream_t st) {
-  constexpr int BT = 16;
-  int RG = 1;
-  while (RG * NS < N) RG <<= 1;
-  const int CH = 128 / RG, NP = RG * NS;
-  const size_t smem = (size_t)(2 * BT * NP + 3 * BT * CH) * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    QSPEC_CUDA(cudaFuncSetAttribute(mamba_scan_kernel<T, NS, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
-  launch_pdl(mamba_scan_kernel<T, NS, BT>, dim3(nseg, (inner + CH - 1) / CH), dim3(128), smem, st, (const T*)x, x_ld, dt_pre, dt_ld, dt_bias,
-             (const T*)bc, bc_ld, (const T*)z, z_ld, A_log, Dp, state, (T*)out, out_ld, meta, seg_starts, ntok, inner, N, RG);
+  constexpr int CH = 128 / RG;
+  launch_pdl(mamba_scan_kernel<T, NS, RG>, dim3(nseg, (inner + CH - 1) / CH), dim3(128), 0, st, (const T*)x, x_ld, dt_pre, dt_ld, dt_bias,
+             (const T*)bc, bc_ld, (const T*)z, z_ld, A_log, Dp, state, (T*)out, out_ld, meta, seg_starts, ntok, inner, N);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
+}
+
+template <typename T>
+static int launch_mamba_n(const void* x, int x_ld, const float* dt_pre, int dt_ld, const float* dt_bias, const void* bc, int bc_ld, const void* z,
+                          int z_ld, const float* A_log, const float* Dp, float* state, void* out, int out_ld, const int* meta,
+                          const int* seg_starts, int nseg, int ntok, int inner, int N, cudaStream_t st) {
+#define MS_ARGS x, x_ld, dt_pre, dt_ld, dt_bias, bc, bc_ld, z, z_ld, A_log, Dp, state, out, out_ld, meta, seg_starts, nseg, ntok, inner, N, st
+  // up to 16 states per thread; larger state sizes spread over 2 .. 32 neighbouring lanes
+  if (N <= 4) return launch_mamba<T, 4, 1>(MS_ARGS);
+  if (N <= 8) return launch_mamba<T, 8, 1>(MS_ARGS);
+  if (N <= 16) return launch_mamba<T, 16, 1>(MS_ARGS);
+  if (N <= 32) return launch_mamba<T, 16, 2>(MS_ARGS);
+  if (N <= 64) return launch_mamba<T, 16, 4>(MS_ARGS);
+  if (N <= 128) return launch_mamba<T, 16, 8>(MS_ARGS);
+  if (N <= 256) return launch_mamba<T, 16, 16>(MS_ARGS);
+  return launch_mamba<T, 16, 32>(MS_ARGS);
+#undef MS_ARGS
 }
 
 extern "C" int qspec_seq_selective_scan(const void* x, int x_ld, const float* dt_pre, int dt_ld, const float* dt_bias, const void* bc,
@@ -584,16 +790,11 @@ extern "C" int qspec_seq_selective_scan(const void* x, int x_ld, const float* dt
   ST_DTYPE_OK(dtype);
   if (ntok == 0 || nseg == 0) return QSPEC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-#define MS_ARGS x, x_ld, dt_pre, dt_ld, dt_bias, bc, bc_ld, z, z_ld, A_log, D_skip, state, out, out_ld, meta, seg_starts, nseg, ntok, inner, N, st
-  if (dtype == QSPEC_DTYPE_F32) {
-    if (N <= 4) return launch_mamba<float, 4>(MS_ARGS);
-    if (N <= 8) return launch_mamba<float, 8>(MS_ARGS);
-    return launch_mamba<float, 16>(MS_ARGS);
-  }
-  if (N <= 4) return launch_mamba<bf16_t, 4>(MS_ARGS);
-  if (N <= 8) return launch_mamba<bf16_t, 8>(MS_ARGS);
-  return launch_mamba<bf16_t, 16>(MS_ARGS);
-#undef MS_ARGS
+  if (dtype == QSPEC_DTYPE_F32)
+    return launch_mamba_n<float>(x, x_ld, dt_pre, dt_ld, dt_bias, bc, bc_ld, z, z_ld, A_log, D_skip, state, out, out_ld, meta, seg_starts, nseg,
+                                 ntok, inner, N, st);
+  return launch_mamba_n<bf16_t>(x, x_ld, dt_pre, dt_ld, dt_bias, bc, bc_ld, z, z_ld, A_log, D_skip, state, out, out_ld, meta, seg_starts, nseg,
+                                ntok, inner, N, st);
 }
 
 extern "C" int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, const float* kn_w, const float* inv_freq, int rot_dims,
@@ -619,44 +820,85 @@ extern "C" int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, cons
   return QSPEC_OK;
 }
 
-template <typename T, int NACC>
-static int launch_talking(const qspec_talking_attn_args* a, cudaStream_t st) {
-  constexpr int BK = 32;
-  const size_t smem = (size_t)(a->H * a->D + a->H * a->H + 2 * a->H * BK + 2 * a->H) * sizeof(float);
-  QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_talking_attention: %zu bytes of shared memory for the queries and the mix", smem);
+template <typename T, int REP, int NQ>
+static int launch_talking(const qspec_talking_attn_args* a, int nsplit, cudaStream_t st) {
+  constexpr int BK = 64;
+  const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3;
+  const size_t smem = (size_t)(NQ * a->H * DP + a->H * HP + 2 * NQ * a->H * BK + NQ * a->H * a->DV + 4 * NQ * a->H) * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    QSPEC_CUDA(cudaFuncSetAttribute(talking_attn_kernel<T, NACC, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    QSPEC_CUDA(cudaFuncSetAttribute(talking_attn_kernel<T, REP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  launch_pdl(talking_attn_kernel<T, NACC, BK>, dim3(a->ntok), dim3(256), smem, st, a->q, (const T*)a->k, a->k_slot_stride, a->k_row_stride,
-             a->k_head_stride, (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->talk, a->sink, (T*)a->out, a->meta,
-             a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale);
-  QSPEC_CHECK_LAUNCH(1);
+  // 16-byte pieces of a key row, two value columns per load: only where every row starts on such a boundary
+  const size_t es = sizeof(T);
+  const int kv = 16 / (int)es;
+  const int vec_k = a->D % kv == 0 && a->k_row_stride % kv == 0 && a->k_head_stride % kv == 0 && a->k_slot_stride % kv == 0 &&
+                    ((uintptr_t)a->k & 15) == 0;
+  const int vec_v = a->v_row_stride % 2 == 0 && a->v_head_stride % 2 == 0 && a->v_slot_stride % 2 == 0 && ((uintptr_t)a->v & (2 * es - 1)) == 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a->ntok + NQ - 1) / NQ, nsplit);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (nsplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = nsplit;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  QSPEC_CUDA(cudaLaunchKernelEx(&cfg, talking_attn_kernel<T, REP, NQ>, a->q, (const T*)a->k, a->k_slot_stride, a->k_row_stride, a->k_head_stride,
+                                (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->talk, a->sink, (T*)a->out, a->meta,
+                                a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale, vec_k, vec_v, nsplit));
+  count_launch(1);
   return QSPEC_OK;
 }
 
-template <typename T>
-static int launch_talking_n(const qspec_talking_attn_args* a, cudaStream_t st) {
-  const long long n = (long long)a->H * a->DV;
-  if (n <= 256) return launch_talking<T, 1>(a, st);
-  if (n <= 512) return launch_talking<T, 2>(a, st);
-  if (n <= 1024) return launch_talking<T, 4>(a, st);
-  if (n <= 2048) return launch_talking<T, 8>(a, st);
-  if (n <= 4096) return launch_talking<T, 16>(a, st);
-  if (n <= 8192) return launch_talking<T, 32>(a, st);
-  QSPEC_REQUIRE(n <= 16384, QSPEC_ERR_UNSUPPORTED, "seq_talking_attention: heads x value size above 16384");
-  return launch_talking<T, 64>(a, st);
+static size_t talking_smem_bytes(const qspec_talking_attn_args* a, int nq) {
+  const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3;
+  return (size_t)(nq * a->H * DP + a->H * HP + 2 * nq * a->H * 64 + nq * a->H * a->DV + 4 * nq * a->H) * sizeof(float);
 }
 
-extern "C" int qspec_seq_talking_attention(const qspec_talking_attn_args* a, int dtype, void* stream) {
+template <typename T>
+static int launch_talking_n(const qspec_talking_attn_args* a, int rows_per_cta, cudaStream_t st) {
+  // the heads of a key/value group share every key and value load: 1, 2, 4 or 8 of them per thread (more in turns)
+  const int rep = a->H / a->G;
+  const bool four = rows_per_cta >= 4 && talking_smem_bytes(a, 4) <= 200 * 1024;
+  QSPEC_REQUIRE(talking_smem_bytes(a, 1) <= 200 * 1024, QSPEC_ERR_UNSUPPORTED,
+                "seq_talking_attention: %zu bytes of shared memory for one token's heads", talking_smem_bytes(a, 1));
+  if (four) {
+    if (rep == 1) return launch_talking<T, 1, 4>(a, 1, st);
+    if (rep == 2) return launch_talking<T, 2, 4>(a, 1, st);
+    if (rep <= 4) return launch_talking<T, 4, 4>(a, 1, st);
+    return launch_talking<T, 8, 4>(a, 1, st);
+  }
+  // one row per CTA: a cluster of four CTAs shares the row's key blocks (the split is fixed, so a token's sums do not depend on
+  // what else the batch holds); QSPEC_SEQ_TALK_SPLIT=1 keeps one CTA per row, for comparison
+  static const int split = [] { const char* v = getenv("QSPEC_SEQ_TALK_SPLIT"); const int n = v ? atoi(v) : 4; return n >= 1 && n <= 8 ? n : 4; }();
+  if (rep == 1) return launch_talking<T, 1, 1>(a, split, st);
+  if (rep == 2) return launch_talking<T, 2, 1>(a, split, st);
+  if (rep <= 4) return launch_talking<T, 4, 1>(a, split, st);
+  return launch_talking<T, 8, 1>(a, split, st);
+}
+
+extern "C" int qspec_seq_talking_attention(const qspec_talking_attn_args* a, int rows_per_cta, int dtype, void* stream) {
   QSPEC_REQUIRE(a && a->q && a->k && a->v && a->talk && a->out && a->meta, QSPEC_ERR_INVALID_ARG, "seq_talking_attention: null pointer");
   QSPEC_REQUIRE(a->ntok >= 0 && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->D > 0 && a->DV > 0 && a->window > 0 && a->cap > 0,
                 QSPEC_ERR_INVALID_ARG, "seq_talking_attention: bad sizes");
   ST_DTYPE_OK(dtype);
   if (a->ntok == 0) return QSPEC_OK;
-  if (dtype == QSPEC_DTYPE_F32) return launch_talking_n<float>(a, (cudaStream_t)stream);
-  return launch_talking_n<bf16_t>(a, (cudaStream_t)stream);
+  if (dtype == QSPEC_DTYPE_F32) return launch_talking_n<float>(a, rows_per_cta, (cudaStream_t)stream);
+  return launch_talking_n<bf16_t>(a, rows_per_cta, (cudaStream_t)stream);
 }
 
 extern "C" int qspec_seq_glu_clamp(const void* gu, int ld, void* out, int ntok, int F, float limit, float alpha, int dtype, void* stream) {

@@ -379,7 +379,10 @@ class KinanexModel(torch.nn.Module):
                          v_norm=True, v_first_in=vf if (m.v_mix and i != first_mixed) else None,
                          v_first_out=vf if (m.v_mix and i == first_mixed) else None, mix=p.vmix)
         att = self.buf_att[:T * H * DV].view(T, H, DV)
-        ops.seq_talking_attention(qf, self.cache_k[i], self.cache_v[i], p.talk, att, tab, FULL_WINDOW, m.scale, sink=p.sink)
+        # prompt portions: four consecutive rows per CTA share the key and value rows they read; decode-shaped steps: a CTA per row
+        rows = 4 if T >= 4 * len(meta.segments) else 1
+        ops.seq_talking_attention(qf, self.cache_k[i], self.cache_v[i], p.talk, att, tab, FULL_WINDOW, m.scale, sink=p.sink,
+                                  rows_per_cta=rows)
         return att.view(T, H * DV)
 
     def _delta(self, i, m, p, h, meta, T):

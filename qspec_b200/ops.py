@@ -1358,12 +1358,14 @@ def seq_gqa_prep(p: torch.Tensor, qn_w: torch.Tensor, kn_w: torch.Tensor, inv_fr
 
 
 def seq_talking_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, talk: torch.Tensor, out: torch.Tensor,
-                          meta: torch.Tensor, window: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+                          meta: torch.Tensor, window: int, scale: float, sink: Optional[torch.Tensor] = None,
+                          rows_per_cta: int = 1) -> None:
     """Softmax attention whose heads' weights are mixed after the softmax: weight_g(j) = exp(s_g(j)) / (exp(sink[g]) + sum_j
     exp(s_g(j))) with s = scale * q_g . k (sink None: no such term); head h applies sum_g talk[h, g] weight_g to the values of its
     own key/value head. q float32 [ntok, H, D]; cache_k [slots, cap, G, D], cache_v [slots, cap, G, DV] (views with a unit last
     stride, row = position % cap); talk float32 [H, H]; out [ntok, H, DV]; a token at position i sees keys j with 0 <= i - j <
-    window."""
+    window. rows_per_cta 4: a CTA takes four consecutive batch rows, which share their key and value loads where they belong to
+    one sequence (prompt portions); 1: one row per CTA (decode-shaped batches)."""
     import ctypes
     _chk(q, "q", (_F32,)); _chk(out, "out", _SEQ_ACT); _chk(talk, "talk", (_F32,)); _chk(sink, "sink", (_F32,), allow_none=True)
     if cache_k.dtype != out.dtype or cache_v.dtype != out.dtype or cache_k.stride(-1) != 1 or cache_v.stride(-1) != 1:
@@ -1377,7 +1379,7 @@ def seq_talking_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch
     a = _lib.TalkingAttnArgs(q.data_ptr(), cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
                              cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), _ptr(talk), _ptr(sink),
                              _ptr(out), _ptr(meta), ntok, H, G, D, DV, int(window), cap, float(scale))
-    _seq(_lib.load_seq().qspec_seq_talking_attention(ctypes.byref(a), _sdt(out), _stream()), "seq_talking_attention")
+    _seq(_lib.load_seq().qspec_seq_talking_attention(ctypes.byref(a), int(rows_per_cta), _sdt(out), _stream()), "seq_talking_attention")
 
 
 def seq_glu_clamp(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> None:

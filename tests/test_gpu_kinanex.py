@@ -273,8 +273,10 @@ def _fill_cache(k, v, slot, slots, cap, dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("H,G,D,DV,n", [(4, 2, 16, 24, 70), (3, 3, 10, 6, 33), (8, 1, 40, 130, 50), (1, 1, 7, 5, 3), (6, 2, 48, 64, 97)])
-def test_attention_with_mixed_heads_and_the_extra_unit_in_the_denominator(dtype, H, G, D, DV, n):
+@pytest.mark.parametrize("rows", [1, 4])
+@pytest.mark.parametrize("H,G,D,DV,n", [(4, 2, 16, 24, 70), (3, 3, 10, 6, 33), (8, 1, 40, 130, 50), (1, 1, 7, 5, 3), (6, 2, 48, 64, 97),
+                                        (20, 2, 8, 3, 150), (12, 4, 128, 128, 140)])
+def test_attention_with_mixed_heads_and_the_extra_unit_in_the_denominator(dtype, H, G, D, DV, n, rows):
     """A prompt portion (the last rows of the sequence) and single tokens against the plain form; rows of other slots and rows
     behind the sequence hold other numbers."""
     _cuda()
@@ -284,13 +286,23 @@ def test_attention_with_mixed_heads_and_the_extra_unit_in_the_denominator(dtype,
     talk = torch.eye(H, dtype=F64) + rnd(g, H, H, scale=0.3)
     scale = 0.8 / math.sqrt(D)
     want = O.talking_attention(q, k, v, talk, scale)
-    ck, cv = _fill_cache(k, v, 1, 3, n + 5, dtype)
+    ck, cv = _fill_cache(k, v, 1, 3, n + 9, dtype)
     sink = torch.zeros(H, dtype=F32, device="cuda")
     first = n // 2
     tab, _ = meta_table([(1, first, n - first, 0)])
     out = torch.empty(n - first, H, DV, dtype=dtype, device="cuda")
-    ops.seq_talking_attention(dev(q[first:]), ck, cv, dev(talk), out, tab, FULL, scale, sink=sink)
+    ops.seq_talking_attention(dev(q[first:]), ck, cv, dev(talk), out, tab, FULL, scale, sink=sink, rows_per_cta=rows)
     close(out, want[first:], dtype, scale=float(want.abs().max()))
+    # rows of two sequences in one step: the second sequence's first rows sit in the CTA that holds the first one's last rows
+    q2, k2, v2 = rnd(g, 9, H, D), rnd(g, 9, G, D, dtype=dtype), rnd(g, 9, G, DV, dtype=dtype)
+    ck[2, :9], cv[2, :9] = dev(k2, dtype), dev(v2, dtype)
+    want2 = O.talking_attention(q2, k2, v2, talk, scale)
+    a = min(n, 6)
+    tab, _ = meta_table([(1, n - a, a, 0), (2, 0, 9, 0)])
+    out2 = torch.empty(a + 9, H, DV, dtype=dtype, device="cuda")
+    ops.seq_talking_attention(dev(torch.cat([q[n - a:], q2])), ck, cv, dev(talk), out2, tab, FULL, scale, sink=sink, rows_per_cta=rows)
+    close(out2[:a], want[n - a:], dtype, scale=float(want.abs().max()))
+    close(out2[a:], want2, dtype, scale=float(want2.abs().max()))
     for t in (0, 1, n - 1):                                                      # the first tokens see almost nothing but the extra unit
         tab, _ = meta_table([(1, t, 1, 0)])
         out = torch.empty(1, H, DV, dtype=dtype, device="cuda")
@@ -304,8 +316,8 @@ def test_attention_with_mixed_heads_and_the_extra_unit_in_the_denominator(dtype,
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("decoded", [False, True])
-def test_a_far_key_among_hundreds_is_found(dtype, decoded):
+@pytest.mark.parametrize("decoded,rows", [(False, 4), (False, 1), (True, 1)])
+def test_a_far_key_among_hundreds_is_found(dtype, decoded, rows):
     """One early key matches the last queries of one head far better than all others, and its value stands out: the output of the
     heads that listen to that head must carry it. A window argument one short of the key's distance must lose it."""
     _cuda()
@@ -322,16 +334,16 @@ def test_a_far_key_among_hundreds_is_found(dtype, decoded):
     assert float(want[n - 1, 2].mean()) > 2.0 and float(want[n - 1, 0].mean()) < -0.5
     ck, cv = _fill_cache(k, v, 0, 1, n, dtype)
     sink = torch.zeros(H, dtype=F32, device="cuda")
-    rows = [n - 1] if decoded else list(range(n - 40, n))
-    tab, _ = meta_table([(0, rows[0], len(rows), 0)])
-    out = torch.empty(len(rows), H, DV, dtype=dtype, device="cuda")
-    ops.seq_talking_attention(dev(q[rows]), ck, cv, dev(talk), out, tab, FULL, 1.0, sink=sink)
-    close(out, want[rows], dtype, scale=float(want[rows].abs().max()))
-    ops.seq_talking_attention(dev(q[rows]), ck, cv, dev(talk), out, tab, n - 1 - far, 1.0, sink=sink)   # sees far + 1 .. only
+    toks = [n - 1] if decoded else list(range(n - 40, n))
+    tab, _ = meta_table([(0, toks[0], len(toks), 0)])
+    out = torch.empty(len(toks), H, DV, dtype=dtype, device="cuda")
+    ops.seq_talking_attention(dev(q[toks]), ck, cv, dev(talk), out, tab, FULL, 1.0, sink=sink, rows_per_cta=rows)
+    close(out, want[toks], dtype, scale=float(want[toks].abs().max()))
+    ops.seq_talking_attention(dev(q[toks]), ck, cv, dev(talk), out, tab, n - 1 - far, 1.0, sink=sink, rows_per_cta=rows)   # sees far + 1 .. only
     assert float(out[-1, 2].float().mean()) < 1.0
-    ops.seq_talking_attention(dev(q[rows]), ck, cv, dev(talk), out, tab, n - far, 1.0, sink=sink)       # the key is the window's first
+    ops.seq_talking_attention(dev(q[toks]), ck, cv, dev(talk), out, tab, n - far, 1.0, sink=sink, rows_per_cta=rows)       # the key is the window's first
     inside = O.talking_attention(q[far:], k[far:], v[far:], talk, 1.0)                                    # the same keys, counted from the window's start
-    close(out[-1], inside[-1], dtype, scale=float(want[rows].abs().max()))
+    close(out[-1], inside[-1], dtype, scale=float(want[toks].abs().max()))
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
