@@ -122,23 +122,26 @@ delta_scan_kernel(const float* __restrict__ cs, int ld, const float* __restrict_
   // rows of the padded unit vectors beyond D stay zero in both buffers
   for (int e = tid; e < 2 * BT * DP; e += 128) { (&sk[0][0][0])[e] = 0.f; (&sq[0][0][0])[e] = 0.f; }
   __syncthreads();
+  // 128 / BT threads per token of the block: no division by a run-time size in the copy loops
+  constexpr int TPT = 128 / BT;
+  const int stt = tid / TPT, sl = tid % TPT;
   auto stage = [&](int buf, int tb) {
-    const int nb = min(BT, mt.seg_end - tb);
-    for (int e = tid; e < nb * D; e += 128) {
-      const int tt = e / D, d = e - tt * D;
-      const float* src = cs + (size_t)(tb + tt) * ld + (size_t)kq * D + d;
-      const int at = (d / NS) * SP + d % NS;
-      cp_async_4(&sq[buf][tt][at], src);
-      cp_async_4(&sk[buf][tt][at], src + GD);
-    }
-    for (int e = tid; e < nb * 16; e += 128) {
-      const int tt = e >> 4, c = e & 15;
-      if (v0 + c < DV) cp_async_4(&sv[buf][tt][c], cs + (size_t)(tb + tt) * ld + 2 * GD + (size_t)h * DV + v0 + c);
-    }
-    for (int e = tid; e < nb * 3; e += 128) {
-      const int tt = e / 3, w = e - tt * 3;
-      const float* gsrc = gates + (size_t)(tb + tt) * NG;
-      cp_async_4(&sg[buf][tt][w], w == 0 ? gsrc + h : (w == 1 ? gsrc + H + h : gsrc + 2 * H + kq));
+    const int t = tb + stt;
+    if (t < mt.seg_end) {
+      const float* src = cs + (size_t)t * ld + (size_t)kq * D;
+      for (int d = sl, at = (sl / NS) * SP + sl % NS; d < D; d += TPT) {
+        cp_async_4(&sq[buf][stt][at], src + d);
+        cp_async_4(&sk[buf][stt][at], src + GD + d);
+        if (TPT % NS == 0) at += (TPT / NS) * SP;                  // the step covers whole row groups
+        else { const int dn = d + TPT; at = (dn / NS) * SP + dn % NS; }
+      }
+      const float* vsrc = cs + (size_t)t * ld + 2 * GD + (size_t)h * DV + v0;
+      for (int c = sl; c < 16; c += TPT)
+        if (v0 + c < DV) cp_async_4(&sv[buf][stt][c], vsrc + c);
+      if (sl < 3) {
+        const float* gsrc = gates + (size_t)t * NG;
+        cp_async_4(&sg[buf][stt][sl], sl == 0 ? gsrc + h : (sl == 1 ? gsrc + H + h : gsrc + 2 * H + kq));
+      }
     }
     cp_async_commit();
   };
@@ -416,7 +419,7 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
     const int g = e / HP, h = e - g * HP;
     stalk[e] = h < H ? talk[h * H + g] : 0.f;
   }
-  const int row0 = blockIdx.x * NQ, rows_end = min(row0 + NQ, ntok);
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * NQ, rows_end = min(row0 + NQ, ntok);   // the batch's last rows see the most keys: first
   const int CP = (DV + 1) / 2, RC = (rep + REP - 1) / REP;
   int first = row0;
   while (first < rows_end) {
