@@ -37,6 +37,19 @@ conv_act_kernel(const T* __restrict__ in, int ld, const float* __restrict__ w, c
   const int first_pos = mt.pos - (i - mt.seg_begin);              // position of the segment's first token
   const float* told = tail + ((size_t)mt.phase * slots + mt.slot) * K1 * C;
   float acc = bias ? bias[c] : 0.f;
+  if (i - mt.seg_begin >= K1 && taps <= 8) {                     // (uniform over the CTA) every tap lies in the step: loads without branches
+    const T* src = in + (size_t)(i - K1) * ld + c;
+    const float* wr = w + (size_t)c * taps;
+    float v[8], ww[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int jc = j < taps ? j : 0;
+      v[j] = to_f(src[(size_t)jc * ld]);
+      ww[j] = j < taps ? wr[jc] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += ww[j] * v[j];
+  } else
   for (int j = 0; j < taps; ++j) {
     const int sp = mt.pos - K1 + j;                                // source position
     float v = 0.f;
@@ -235,12 +248,6 @@ mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ d
   const int n0 = rg * NS;
   float S[NS], A[NS];
   float* st = state + ((size_t)mt.slot * inner + (live ? c : 0)) * N;
-#pragma unroll
-  for (int r = 0; r < NS; ++r) {
-    const bool ok = live && n0 + r < N;
-    A[r] = ok ? -expf(A_log[(size_t)c * N + n0 + r]) : 0.f;
-    S[r] = (ok && mt.pos > 0) ? st[n0 + r] : 0.f;
-  }
   float rx[XR], rd[XR], rz[XR], rb[BR], rc[BR];
   // every load of a block is issued before the first one is used: addresses outside the block are clamped into it rather than
   // skipped (a branch around a load would make the loads wait for one another), and what they bring is never used
@@ -263,7 +270,14 @@ mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ d
       rc[r] = n < N ? cc : 0.f;
     }
   };
-  fetch(mt.seg_begin);
+  fetch(mt.seg_begin);                                           // in flight while the state and the decay rates arrive
+#pragma unroll
+  for (int r = 0; r < NS; ++r) {
+    const bool ok = live && n0 + r < N;
+    // exp(dt A) = 2^(dt A log2 e): the rate is stored times log2 e, so that the token loop pays one multiply and one exp2
+    A[r] = ok ? -expf(A_log[(size_t)c * N + n0 + r]) * 1.4426950408889634f : 0.f;
+    S[r] = (ok && mt.pos > 0) ? st[n0 + r] : 0.f;
+  }
   for (int tb = mt.seg_begin; tb < mt.seg_end; tb += BT) {
     const int nb = min(BT, mt.seg_end - tb);
 #pragma unroll
@@ -290,10 +304,10 @@ mamba_scan_kernel(const T* __restrict__ x, int x_ld, const float* __restrict__ d
 #pragma unroll
       for (int r = 0; r < NS / 4; ++r) {
         const float4 b = B4[r], cq = C4[r];
-        S[4 * r] = expf(dt * A[4 * r]) * S[4 * r] + dx * b.x;             y0 += S[4 * r] * cq.x;
-        S[4 * r + 1] = expf(dt * A[4 * r + 1]) * S[4 * r + 1] + dx * b.y; y1 += S[4 * r + 1] * cq.y;
-        S[4 * r + 2] = expf(dt * A[4 * r + 2]) * S[4 * r + 2] + dx * b.z; y0 += S[4 * r + 2] * cq.z;
-        S[4 * r + 3] = expf(dt * A[4 * r + 3]) * S[4 * r + 3] + dx * b.w; y1 += S[4 * r + 3] * cq.w;
+        S[4 * r] = exp2f(dt * A[4 * r]) * S[4 * r] + dx * b.x;             y0 += S[4 * r] * cq.x;
+        S[4 * r + 1] = exp2f(dt * A[4 * r + 1]) * S[4 * r + 1] + dx * b.y; y1 += S[4 * r + 1] * cq.y;
+        S[4 * r + 2] = exp2f(dt * A[4 * r + 2]) * S[4 * r + 2] + dx * b.z; y0 += S[4 * r + 2] * cq.z;
+        S[4 * r + 3] = exp2f(dt * A[4 * r + 3]) * S[4 * r + 3] + dx * b.w; y1 += S[4 * r + 3] * cq.w;
       }
       float y = y0 + y1;
 #pragma unroll
@@ -328,13 +342,17 @@ gqa_prep_kernel(const T* __restrict__ p, int ld, const float* __restrict__ qn_w,
                 const float* __restrict__ mix, float* __restrict__ qout, T* __restrict__ cache_k, T* __restrict__ cache_v, int cap,
                 const int* __restrict__ meta, int ntok, int H, int G, int D, int DV, float eps, int v_norm) {
   pdl_enter();
-  extern __shared__ float sm_gp[];                                // one row of max(D, DV) per warp
+  extern __shared__ float sm_gp[];                                // one row of max(D, DV) per warp | cos [half] | sin [half]
   const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slot = meta[i], pos = meta[ntok + i];
   const int DM = max(D, DV);
   float* buf = sm_gp + warp * DM;
   const T* row = p + (size_t)i * ld;
   const int half = rot_dims / 2;
+  float* s_cos = sm_gp + 4 * DM;
+  float* s_sin = s_cos + half;
+  for (int f = threadIdx.x; f < half; f += 128) sincosf((float)pos * inv_freq[f], &s_sin[f], &s_cos[f]);   // once per token, for all heads
+  __syncthreads();
   const size_t crow = (size_t)slot * cap + (size_t)(pos % cap);
   for (int hh = warp; hh < H + G; hh += 4) {                      // query heads, then key heads
     const bool isq = hh < H;
@@ -352,8 +370,7 @@ gqa_prep_kernel(const T* __restrict__ p, int ld, const float* __restrict__ qn_w,
       float v = buf[c];
       if (c < 2 * half) {
         const int f = c < half ? c : c - half;
-        float sn, cs;
-        sincosf((float)pos * inv_freq[f], &sn, &cs);
+        const float sn = s_sin[f], cs = s_cos[f];
         v = c < half ? buf[c] * cs - buf[c + half] * sn : buf[c] * cs + buf[c - half] * sn;
       }
       if (isq) qdst[c] = v; else kdst[c] = from_f<T>(v);
@@ -810,8 +827,8 @@ extern "C" int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, cons
                 rot_dims <= D && ld >= (H + G) * D + G * DV, QSPEC_ERR_INVALID_ARG, "seq_gqa_prep: bad sizes");
   ST_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
-  const size_t smem = (size_t)4 * (D > DV ? D : DV) * sizeof(float);
-  QSPEC_REQUIRE(smem <= 48 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_gqa_prep: head size above 3072");
+  const size_t smem = ((size_t)4 * (D > DV ? D : DV) + rot_dims) * sizeof(float);
+  QSPEC_REQUIRE(smem <= 48 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_gqa_prep: head size above 2048");
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == QSPEC_DTYPE_F32)
     launch_pdl(gqa_prep_kernel<float>, dim3(ntok), dim3(128), smem, st, (const float*)p, ld, qn_w, kn_w, inv_freq, rot_dims, v_first_in,
