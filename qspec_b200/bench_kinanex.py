@@ -95,8 +95,9 @@ def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
         qs = [torch.randn(T, H, D, device=dev) * 0.3 for _ in range(2)]
         out = torch.empty(T, H, D, device=dev, dtype=bf)
         visible = sum(p + 1 for _, p0, n in segs for p in range(p0, p0 + n))
-        us = _time_us(torch, [lambda i=i: ops.seq_talking_attention(qs[i % 2], ck[i % 2], cv[i % 2], talk, out, tab, full, D ** -0.5, sink=sink)
-                              for i in range(2)], reps=6 if label == "prompt" else 20)
+        rows_per_cta = 4 if label == "prompt" else 1            # what the model passes for these step shapes
+        us = _time_us(torch, [lambda i=i: ops.seq_talking_attention(qs[i % 2], ck[i % 2], cv[i % 2], talk, out, tab, full, D ** -0.5, sink=sink,
+                                                                    rows_per_cta=rows_per_cta) for i in range(2)], reps=6 if label == "prompt" else 20)
         if label == "prompt":
             add("seq_talking_attention (two passes, heads mixed after the softmax), causal over the whole prompt",
                 f"T={T} H={H} G={G} key {D} value {D}", us, flops=2.0 * visible * H * (2 * D + H))

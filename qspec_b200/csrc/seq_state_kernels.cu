@@ -16,6 +16,21 @@ __device__ __forceinline__ void cp_async_4(float* smem_dst, const float* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// 16-byte asynchronous copy into shared memory; `valid` false writes zeros and reads nothing
+__device__ __forceinline__ void cp_async_16z(void* smem_dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src),
+               "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void tk_ldmatrix_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void tk_mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -416,14 +431,20 @@ __global__ void __launch_bounds__(256)
 talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long long k_ss, int k_rs, int k_hs,
                     const T* __restrict__ vc, long long v_ss, int v_rs, int v_hs, const float* __restrict__ talk,
                     const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G, int D,
-                    int DV, int window, int cap, float scale, int vec_k, int vec_v, int nsplit) {
+                    int DV, int window, int cap, float scale, int vec_k, int vec_v, int nsplit, int tc_gc) {
   pdl_enter();
   constexpr int BK = 64, KV = 16 / (int)sizeof(T);                // keys per block; elements of a 16-byte piece
   extern __shared__ __align__(16) float sm_ta[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int HP = (H + 3) & ~3, DP = (D + 3) & ~3, rep = H / G;
-  float* sq = sm_ta;                                              // [NQ][H][DP]
-  float* stalk = sq + NQ * H * DP;                                // [H][HP]: stalk[g][h] = talk[h][g]
+  // tc_gc > 0 (bfloat16, NQ = 4): the scores of both passes come from the tensor cores. The queries wait as bfloat16 rows
+  // [key/value head][16 MT rows = (token, head of the group)][D + 8], the key rows of tc_gc key/value heads and one block at a time
+  // as [head][key][D + 8] (cp.async); a warp takes 16 rows x 16 keys at a time with ldmatrix + mma.sync and writes float32 scores.
+  constexpr int MT = (NQ * REP + 15) / 16;
+  const bool tc = sizeof(T) == 2 && NQ == 4 && tc_gc > 0;
+  const int DQ = D + 8;
+  float* sq = sm_ta;                                              // [NQ][H][DP] (CUDA-core scores only)
+  float* stalk = sq + (tc ? 0 : NQ * H * DP);                     // [H][HP]: stalk[g][h] = talk[h][g]
   float* sS = stalk + H * HP;                                     // [NQ][H][BK]
   float* sW = sS + NQ * H * BK;                                   // [NQ][H][BK]
   float* sO = sW + NQ * H * BK;                                   // [NQ][H][DV]
@@ -431,6 +452,8 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
   float* srl = smx + NQ * H;                                      // [NQ][H] denominators, then their reciprocals
   float* spm = srl + NQ * H;                                      // [NQ][H] this CTA's own maxima / denominators, read by its cluster
   float* spl = spm + NQ * H;
+  __nv_bfloat16* sQb = reinterpret_cast<__nv_bfloat16*>(spl + NQ * H);      // [G][16 MT][DQ]
+  __nv_bfloat16* sKb = sQb + (size_t)G * 16 * MT * DQ;                       // [tc_gc][BK][DQ]
   const int rank = blockIdx.y;
   for (int e = tid; e < H * HP; e += 256) {
     const int g = e / HP, h = e - g * HP;
@@ -446,9 +469,17 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
     const int posl = pos0 + nq - 1;
     const int j0 = max(0, pos0 - window + 1);
     __syncthreads();                                             // the previous group is done with the shared buffers
-    for (int e = tid; e < nq * H * DP; e += 256) {
-      const int r = e / DP, c = e - r * DP;
-      sq[e] = c < D ? q[((size_t)first * H + r) * D + c] * scale : 0.f;
+    if (tc) {
+      for (int e = tid; e < G * 16 * MT * DQ; e += 256) {
+        const int c = e % DQ, t = e / DQ, rho = t % (16 * MT), kg = t / (16 * MT), a = rho / REP, r = rho % REP;
+        const bool ok = c < D && a < nq && r < rep;
+        sQb[e] = __float2bfloat16_rn(ok ? q[((size_t)(first + a) * H + kg * rep + r) * D + c] * scale : 0.f);
+      }
+    } else {
+      for (int e = tid; e < nq * H * DP; e += 256) {
+        const int r = e / DP, c = e - r * DP;
+        sq[e] = c < D ? q[((size_t)first * H + r) * D + c] * scale : 0.f;
+      }
     }
     for (int e = tid; e < nq * H; e += 256) {                    // the sink's term is counted once: by rank 0
       const bool sk = sink && rank == 0;
@@ -461,6 +492,49 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
     const T* vbase = vc + (size_t)slot * v_ss;
 
     auto scores = [&](int jb) {
+      if (tc) {
+        const int gid = lane >> 2, tig = lane & 3, np8 = D / 8;
+        for (int kg0 = 0; kg0 < G; kg0 += tc_gc) {
+          const int gcn = min(tc_gc, G - kg0);
+          __syncthreads();                                         // the tile's previous readers are done
+          for (int e = tid; e < gcn * BK * np8; e += 256) {
+            const int pc = e % np8, t = e / np8, jj = t % BK, kgl = t / BK, j = min(jb + jj, posl);
+            cp_async_16z(sKb + ((size_t)(kgl * BK + jj) * DQ + pc * 8),
+                         kbase + (size_t)(j < cap ? j : j % cap) * k_rs + (size_t)(kg0 + kgl) * k_hs + pc * 8, jb + jj <= posl);
+          }
+          cp_async_commit();
+          cp_async_wait<0>();
+          __syncthreads();
+          for (int u = warp; u < gcn * MT * (BK / 16); u += 8) {
+            const int np = u % (BK / 16), t = u / (BK / 16), mt = t % MT, kgl = t / MT, kg = kg0 + kgl;
+            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            const __nv_bfloat16* qa = sQb + ((size_t)(kg * MT + mt) * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DQ + 8 * (lane >> 4);
+            const __nv_bfloat16* kb = sKb + ((size_t)kgl * BK + np * 16 + (lane & 7) + 8 * (lane >> 4)) * DQ + 8 * ((lane >> 3) & 1);
+            for (int ks = 0; ks < D / 16; ++ks) {
+              uint32_t af[4], bfr[4];
+              tk_ldmatrix_x4(af, qa + ks * 16);
+              tk_ldmatrix_x4(bfr, kb + ks * 16);
+              tk_mma_16816(c0, af, bfr[0], bfr[1]);
+              tk_mma_16816(c1, af, bfr[2], bfr[3]);
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int rho = mt * 16 + gid + 8 * half, a = rho / REP, r = rho % REP;
+              if (a < nq && r < rep) {
+                const int pa = pos0 + a;
+                float* dst = sS + (a * H + kg * rep + r) * BK + np * 16 + 2 * tig;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {                       // x: (second eight keys, odd column)
+                  const int jj = np * 16 + 8 * (x >> 1) + 2 * tig + (x & 1), j = jb + jj;
+                  const float val = (x >> 1) ? c1[2 * half + (x & 1)] : c0[2 * half + (x & 1)];
+                  dst[8 * (x >> 1) + (x & 1)] = (j <= pa && pa - j < window) ? val : -INFINITY;
+                }
+              }
+            }
+          }
+        }
+        return;
+      }
       for (int e = tid; e < BK * G; e += 256) {
         const int kg = e / BK, jj = e - kg * BK, j = jb + jj;
         float d[NQ][REP];
@@ -840,11 +914,17 @@ extern "C" int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, cons
   return QSPEC_OK;
 }
 
+// Shared memory of talking_attn_kernel: tc_gc > 0 replaces the float32 queries by bfloat16 query rows and a key tile.
+static size_t talking_smem_bytes(const qspec_talking_attn_args* a, int nq, int rep_t, int tc_gc) {
+  const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3, mt = (nq * rep_t + 15) / 16;
+  size_t fl = (size_t)a->H * HP + 2 * (size_t)nq * a->H * 64 + (size_t)nq * a->H * a->DV + 4 * (size_t)nq * a->H;
+  if (tc_gc <= 0) return (fl + (size_t)nq * a->H * DP) * sizeof(float);
+  return fl * sizeof(float) + ((size_t)a->G * 16 * mt + (size_t)tc_gc * 64) * (a->D + 8) * 2;
+}
+
 template <typename T, int REP, int NQ>
-static int launch_talking(const qspec_talking_attn_args* a, int nsplit, cudaStream_t st) {
-  constexpr int BK = 64;
-  const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3;
-  const size_t smem = (size_t)(NQ * a->H * DP + a->H * HP + 2 * NQ * a->H * BK + NQ * a->H * a->DV + 4 * NQ * a->H) * sizeof(float);
+static int launch_talking(const qspec_talking_attn_args* a, int nsplit, int tc_gc, cudaStream_t st) {
+  const size_t smem = talking_smem_bytes(a, NQ, REP, tc_gc);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     QSPEC_CUDA(cudaFuncSetAttribute(talking_attn_kernel<T, REP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -879,36 +959,42 @@ static int launch_talking(const qspec_talking_attn_args* a, int nsplit, cudaStre
   cfg.numAttrs = na;
   QSPEC_CUDA(cudaLaunchKernelEx(&cfg, talking_attn_kernel<T, REP, NQ>, a->q, (const T*)a->k, a->k_slot_stride, a->k_row_stride, a->k_head_stride,
                                 (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->talk, a->sink, (T*)a->out, a->meta,
-                                a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale, vec_k, vec_v, nsplit));
+                                a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale, vec_k, vec_v, nsplit, tc_gc));
   count_launch(1);
   return QSPEC_OK;
-}
-
-static size_t talking_smem_bytes(const qspec_talking_attn_args* a, int nq) {
-  const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3;
-  return (size_t)(nq * a->H * DP + a->H * HP + 2 * nq * a->H * 64 + nq * a->H * a->DV + 4 * nq * a->H) * sizeof(float);
 }
 
 template <typename T>
 static int launch_talking_n(const qspec_talking_attn_args* a, int rows_per_cta, cudaStream_t st) {
   // the heads of a key/value group share every key and value load: 1, 2, 4 or 8 of them per thread (more in turns)
   const int rep = a->H / a->G;
-  const bool four = rows_per_cta >= 4 && talking_smem_bytes(a, 4) <= 200 * 1024;
-  QSPEC_REQUIRE(talking_smem_bytes(a, 1) <= 200 * 1024, QSPEC_ERR_UNSUPPORTED,
-                "seq_talking_attention: %zu bytes of shared memory for one token's heads", talking_smem_bytes(a, 1));
-  if (four) {
-    if (rep == 1) return launch_talking<T, 1, 4>(a, 1, st);
-    if (rep == 2) return launch_talking<T, 2, 4>(a, 1, st);
-    if (rep <= 4) return launch_talking<T, 4, 4>(a, 1, st);
-    return launch_talking<T, 8, 4>(a, 1, st);
+  const int rep_t = rep == 1 ? 1 : rep == 2 ? 2 : rep <= 4 ? 4 : 8;
+  const size_t limit = 200 * 1024;
+  const bool four = rows_per_cta >= 4 && talking_smem_bytes(a, 4, rep_t, 0) <= limit;
+  QSPEC_REQUIRE(talking_smem_bytes(a, 1, rep_t, 0) <= limit, QSPEC_ERR_UNSUPPORTED,
+                "seq_talking_attention: %zu bytes of shared memory for one token's heads", talking_smem_bytes(a, 1, rep_t, 0));
+  // bfloat16 prompt portions whose key rows are whole 16-byte pieces take their scores from the tensor cores, with as many
+  // key/value heads per key tile as shared memory holds; QSPEC_SEQ_TALK_TC=0 keeps the CUDA-core scores, for comparison
+  static const bool tc_on = [] { const char* v = getenv("QSPEC_SEQ_TALK_TC"); return !(v && v[0] == '0'); }();
+  int tc_gc = 0;
+  if (sizeof(T) == 2 && rows_per_cta >= 4 && tc_on && rep <= 8 && a->D % 16 == 0 && a->k_row_stride % 8 == 0 && a->k_head_stride % 8 == 0 &&
+      a->k_slot_stride % 8 == 0 && ((uintptr_t)a->k & 15) == 0) {
+    for (int gc = a->G < 4 ? a->G : 4; gc >= 1 && !tc_gc; gc >>= 1)
+      if (talking_smem_bytes(a, 4, rep_t, gc) <= 224 * 1024) tc_gc = gc;
+  }
+  if (four || tc_gc) {
+    if (rep == 1) return launch_talking<T, 1, 4>(a, 1, tc_gc, st);
+    if (rep == 2) return launch_talking<T, 2, 4>(a, 1, tc_gc, st);
+    if (rep <= 4) return launch_talking<T, 4, 4>(a, 1, tc_gc, st);
+    return launch_talking<T, 8, 4>(a, 1, tc_gc, st);
   }
   // one row per CTA: a cluster of four CTAs shares the row's key blocks (the split is fixed, so a token's sums do not depend on
   // what else the batch holds); QSPEC_SEQ_TALK_SPLIT=1 keeps one CTA per row, for comparison
   static const int split = [] { const char* v = getenv("QSPEC_SEQ_TALK_SPLIT"); const int n = v ? atoi(v) : 4; return n >= 1 && n <= 8 ? n : 4; }();
-  if (rep == 1) return launch_talking<T, 1, 1>(a, split, st);
-  if (rep == 2) return launch_talking<T, 2, 1>(a, split, st);
-  if (rep <= 4) return launch_talking<T, 4, 1>(a, split, st);
-  return launch_talking<T, 8, 1>(a, split, st);
+  if (rep == 1) return launch_talking<T, 1, 1>(a, split, 0, st);
+  if (rep == 2) return launch_talking<T, 2, 1>(a, split, 0, st);
+  if (rep <= 4) return launch_talking<T, 4, 1>(a, split, 0, st);
+  return launch_talking<T, 8, 1>(a, split, 0, st);
 }
 
 extern "C" int qspec_seq_talking_attention(const qspec_talking_attn_args* a, int rows_per_cta, int dtype, void* stream) {
