@@ -25,6 +25,19 @@ __device__ __forceinline__ void tk_ldmatrix_x4(uint32_t (&r)[4], const __nv_bflo
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+__device__ __forceinline__ void tk_ldmatrix_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+// (hi, lo) split of two float32 weights: hi = bf16(w), lo = bf16(w - hi); hi + lo carries 16 mantissa bits
+__device__ __forceinline__ void tk_split_bf2(float w0, float w1, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
+  __nv_bfloat162 hv, lv;
+  hv.x = h0; hv.y = h1;
+  lv = __floats2bfloat162_rn(w0 - __bfloat162float(h0), w1 - __bfloat162float(h1));
+  hi = *reinterpret_cast<uint32_t*>(&hv);
+  lo = *reinterpret_cast<uint32_t*>(&lv);
+}
 __device__ __forceinline__ void tk_mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -431,7 +444,7 @@ __global__ void __launch_bounds__(256)
 talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long long k_ss, int k_rs, int k_hs,
                     const T* __restrict__ vc, long long v_ss, int v_rs, int v_hs, const float* __restrict__ talk,
                     const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G, int D,
-                    int DV, int window, int cap, float scale, int vec_k, int vec_v, int nsplit, int tc_gc) {
+                    int DV, int window, int cap, float scale, int vec_k, int vec_v, int nsplit, int tc_gc, int pv_tc) {
   pdl_enter();
   constexpr int BK = 64, KV = 16 / (int)sizeof(T);                // keys per block; elements of a 16-byte piece
   extern __shared__ __align__(16) float sm_ta[];
@@ -440,8 +453,15 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
   // tc_gc > 0 (bfloat16, NQ = 4): the scores of both passes come from the tensor cores. The queries wait as bfloat16 rows
   // [key/value head][16 MT rows = (token, head of the group)][D + 8], the key rows of tc_gc key/value heads and one block at a time
   // as [head][key][D + 8] (cp.async); a warp takes 16 rows x 16 keys at a time with ldmatrix + mma.sync and writes float32 scores.
+  // pv_tc: the value products too: the mixed weights leave shared memory as a two-term bfloat16 split (rows = the same 16-row
+  // tiles), the value rows of a block come in as [head][key][DV + 8] and are read transposed; a warp owns up to eight tiles of
+  // 16 rows x 16 value columns, whose sums stay in its registers over all key blocks.
   constexpr int MT = (NQ * REP + 15) / 16;
-  const bool tc = sizeof(T) == 2 && NQ == 4 && tc_gc > 0;
+  constexpr bool TCK = sizeof(T) == 2 && NQ == 4;
+  constexpr int UPW = TCK ? 8 : 1;
+  const bool tc = TCK && tc_gc > 0;
+  const bool pv = tc && pv_tc;
+  float oacc[UPW][2][4];
   const int DQ = D + 8;
   float* sq = sm_ta;                                              // [NQ][H][DP] (CUDA-core scores only)
   float* stalk = sq + (tc ? 0 : NQ * H * DP);                     // [H][HP]: stalk[g][h] = talk[h][g]
@@ -487,6 +507,10 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
       srl[e] = sk ? 1.f : 0.f;
     }
     for (int e = tid; e < nq * H * DV; e += 256) sO[e] = 0.f;
+#pragma unroll
+    for (int i = 0; i < UPW; ++i)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) oacc[i][0][x] = oacc[i][1][x] = 0.f;
     __syncthreads();
     const T* kbase = kc + (size_t)slot * k_ss;
     const T* vbase = vc + (size_t)slot * v_ss;
@@ -647,10 +671,22 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
     }
     for (int e = tid; e < nq * H; e += 256) srl[e] = srl[e] > 0.f ? 1.0f / srl[e] : 0.f;
     __syncthreads();
+    // value rows of a block into the tile buffer (once the scores' products have read the key rows out of it)
+    auto load_values = [&](int jb, int kg0, int gcn) {
+      const int DVQ = DV + 8, np8v = DV / 8;
+      for (int e = tid; e < gcn * BK * np8v; e += 256) {
+        const int pc = e % np8v, t = e / np8v, jj = t % BK, kgl = t / BK, j = min(jb + jj, posl);
+        cp_async_16z(sKb + ((size_t)(kgl * BK + jj) * DVQ + pc * 8),
+                     vbase + (size_t)(j < cap ? j : j % cap) * v_rs + (size_t)(kg0 + kgl) * v_hs + pc * 8, jb + jj <= posl);
+      }
+      cp_async_commit();
+    };
+    const bool v_ahead = pv && tc_gc >= G;                        // one tile holds all heads: the values travel while the weights are mixed
     // pass 2: weights, mix, values
     for (int jb = j0 + rank * BK; jb <= posl; jb += nsplit * BK) {
       scores(jb);
       __syncthreads();
+      if (v_ahead) load_values(jb, 0, G);
       for (int e = tid; e < nq * H * BK; e += 256) {
         const int r = e / BK;
         sS[e] = expf(sS[e] - smx[r]) * srl[r];                    // exp(-inf) = 0 for keys a row does not see
@@ -672,6 +708,50 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
       }
       __syncthreads();
       const int nk = min(BK, posl - jb + 1);
+      if (TCK && pv) {
+        const int gid = lane >> 2, tig = lane & 3, DVQ = DV + 8, ndp = DV / 16;
+        for (int kg0 = 0; kg0 < G; kg0 += tc_gc) {
+          const int gcn = min(tc_gc, G - kg0);
+          if (!v_ahead) {
+            __syncthreads();                                       // the tile's previous readers are done
+            load_values(jb, kg0, gcn);
+          }
+          cp_async_wait<0>();
+          __syncthreads();
+#pragma unroll
+          for (int i = 0; i < UPW; ++i) {
+            const int u = warp + 8 * i;
+            if (u >= G * MT * ndp) continue;
+            const int dp = u % ndp, t = u / ndp, mt = t % MT, kg = t / MT;
+            if (kg < kg0 || kg >= kg0 + gcn) continue;
+            const int rho0 = mt * 16 + gid, rho1 = rho0 + 8;
+            const bool ok0 = rho0 / REP < nq && rho0 % REP < rep, ok1 = rho1 / REP < nq && rho1 % REP < rep;
+            const float* w0 = sW + ((rho0 / REP) * H + kg * rep + rho0 % REP) * BK + 2 * tig;
+            const float* w1 = sW + ((rho1 / REP) * H + kg * rep + rho1 % REP) * BK + 2 * tig;
+            const __nv_bfloat16* vt = sKb + ((size_t)(kg - kg0) * BK + (lane & 7) + 8 * ((lane >> 3) & 1)) * DVQ + dp * 16 + 8 * (lane >> 4);
+            const float2 zero = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              const float2 a00 = ok0 ? *reinterpret_cast<const float2*>(w0 + kk * 16) : zero;
+              const float2 a01 = ok0 ? *reinterpret_cast<const float2*>(w0 + kk * 16 + 8) : zero;
+              const float2 a10 = ok1 ? *reinterpret_cast<const float2*>(w1 + kk * 16) : zero;
+              const float2 a11 = ok1 ? *reinterpret_cast<const float2*>(w1 + kk * 16 + 8) : zero;
+              uint32_t ah[4], al[4], b[4];
+              tk_split_bf2(a00.x, a00.y, ah[0], al[0]);
+              tk_split_bf2(a10.x, a10.y, ah[1], al[1]);
+              tk_split_bf2(a01.x, a01.y, ah[2], al[2]);
+              tk_split_bf2(a11.x, a11.y, ah[3], al[3]);
+              tk_ldmatrix_x4_trans(b, vt + (size_t)kk * 16 * DVQ);
+              tk_mma_16816(oacc[i][0], ah, b[0], b[1]);
+              tk_mma_16816(oacc[i][0], al, b[0], b[1]);
+              tk_mma_16816(oacc[i][1], ah, b[2], b[3]);
+              tk_mma_16816(oacc[i][1], al, b[2], b[3]);
+            }
+          }
+        }
+        __syncthreads();
+        continue;
+      }
       for (int e = tid; e < G * RC * CP; e += 256) {
         const int cp = e % CP, t = e / CP, rc = t % RC, kg = t / RC;
         const int c = 2 * cp, h0 = kg * rep + rc * REP, nr = min(REP, rep - rc * REP);
@@ -747,6 +827,22 @@ talking_attn_kernel(const float* __restrict__ q, const T* __restrict__ kc, long 
         out[(size_t)first * H * DV + e] = from_f<T>(v);
       }
       cluster_sync_all();                                        // nobody leaves while its partial sums may still be read
+    } else if (TCK && pv) {
+      const int gid = lane >> 2, tig = lane & 3, ndp = DV / 16;
+#pragma unroll
+      for (int i = 0; i < UPW; ++i) {
+        const int u = warp + 8 * i;
+        if (u >= G * MT * ndp) continue;
+        const int dp = u % ndp, t = u / ndp, mt = t % MT, kg = t / MT;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int rho = mt * 16 + gid + 8 * half, a = rho / REP, r = rho % REP;
+          if (a >= nq || r >= rep) continue;
+          T* orow = out + ((size_t)(first + a) * H + kg * rep + r) * DV + dp * 16 + 2 * tig;
+          orow[0] = from_f<T>(oacc[i][0][2 * half]);     orow[1] = from_f<T>(oacc[i][0][2 * half + 1]);
+          orow[8] = from_f<T>(oacc[i][1][2 * half]);     orow[9] = from_f<T>(oacc[i][1][2 * half + 1]);
+        }
+      }
     } else {
       for (int e = tid; e < nq * H * DV; e += 256) out[(size_t)first * H * DV + e] = from_f<T>(sO[e]);
     }
@@ -915,16 +1011,17 @@ extern "C" int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, cons
 }
 
 // Shared memory of talking_attn_kernel: tc_gc > 0 replaces the float32 queries by bfloat16 query rows and a key tile.
-static size_t talking_smem_bytes(const qspec_talking_attn_args* a, int nq, int rep_t, int tc_gc) {
+static size_t talking_smem_bytes(const qspec_talking_attn_args* a, int nq, int rep_t, int tc_gc, int pv_tc = 0) {
   const int HP = (a->H + 3) & ~3, DP = (a->D + 3) & ~3, mt = (nq * rep_t + 15) / 16;
   size_t fl = (size_t)a->H * HP + 2 * (size_t)nq * a->H * 64 + (size_t)nq * a->H * a->DV + 4 * (size_t)nq * a->H;
   if (tc_gc <= 0) return (fl + (size_t)nq * a->H * DP) * sizeof(float);
-  return fl * sizeof(float) + ((size_t)a->G * 16 * mt + (size_t)tc_gc * 64) * (a->D + 8) * 2;
+  const int dt = pv_tc && a->DV > a->D ? a->DV : a->D;          // the tile buffer holds key rows, then value rows
+  return fl * sizeof(float) + (size_t)a->G * 16 * mt * (a->D + 8) * 2 + (size_t)tc_gc * 64 * (dt + 8) * 2;
 }
 
 template <typename T, int REP, int NQ>
-static int launch_talking(const qspec_talking_attn_args* a, int nsplit, int tc_gc, cudaStream_t st) {
-  const size_t smem = talking_smem_bytes(a, NQ, REP, tc_gc);
+static int launch_talking(const qspec_talking_attn_args* a, int nsplit, int tc_gc, int pv_tc, cudaStream_t st) {
+  const size_t smem = talking_smem_bytes(a, NQ, REP, tc_gc, pv_tc);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     QSPEC_CUDA(cudaFuncSetAttribute(talking_attn_kernel<T, REP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -959,7 +1056,7 @@ static int launch_talking(const qspec_talking_attn_args* a, int nsplit, int tc_g
   cfg.numAttrs = na;
   QSPEC_CUDA(cudaLaunchKernelEx(&cfg, talking_attn_kernel<T, REP, NQ>, a->q, (const T*)a->k, a->k_slot_stride, a->k_row_stride, a->k_head_stride,
                                 (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->talk, a->sink, (T*)a->out, a->meta,
-                                a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale, vec_k, vec_v, nsplit, tc_gc));
+                                a->ntok, a->H, a->G, a->D, a->DV, a->window, a->cap, a->scale, vec_k, vec_v, nsplit, tc_gc, pv_tc));
   count_launch(1);
   return QSPEC_OK;
 }
@@ -976,25 +1073,31 @@ static int launch_talking_n(const qspec_talking_attn_args* a, int rows_per_cta, 
   // bfloat16 prompt portions whose key rows are whole 16-byte pieces take their scores from the tensor cores, with as many
   // key/value heads per key tile as shared memory holds; QSPEC_SEQ_TALK_TC=0 keeps the CUDA-core scores, for comparison
   static const bool tc_on = [] { const char* v = getenv("QSPEC_SEQ_TALK_TC"); return !(v && v[0] == '0'); }();
-  int tc_gc = 0;
+  int tc_gc = 0, pv_tc = 0;
+  static const bool pv_on = [] { const char* v = getenv("QSPEC_SEQ_TALK_PV_TC"); return !(v && v[0] == '0'); }();
   if (sizeof(T) == 2 && rows_per_cta >= 4 && tc_on && rep <= 8 && a->D % 16 == 0 && a->k_row_stride % 8 == 0 && a->k_head_stride % 8 == 0 &&
       a->k_slot_stride % 8 == 0 && ((uintptr_t)a->k & 15) == 0) {
+    // value products on the tensor cores too where the value rows are whole 16-byte pieces and eight tiles per warp hold them
+    const int mt = (4 * rep_t + 15) / 16;
+    pv_tc = pv_on && a->DV % 16 == 0 && a->v_row_stride % 8 == 0 && a->v_head_stride % 8 == 0 && a->v_slot_stride % 8 == 0 &&
+            ((uintptr_t)a->v & 15) == 0 && a->G * mt * (a->DV / 16) <= 64;
     for (int gc = a->G < 4 ? a->G : 4; gc >= 1 && !tc_gc; gc >>= 1)
-      if (talking_smem_bytes(a, 4, rep_t, gc) <= 224 * 1024) tc_gc = gc;
+      if (talking_smem_bytes(a, 4, rep_t, gc, pv_tc) <= 224 * 1024) tc_gc = gc;
+    if (!tc_gc) pv_tc = 0;
   }
   if (four || tc_gc) {
-    if (rep == 1) return launch_talking<T, 1, 4>(a, 1, tc_gc, st);
-    if (rep == 2) return launch_talking<T, 2, 4>(a, 1, tc_gc, st);
-    if (rep <= 4) return launch_talking<T, 4, 4>(a, 1, tc_gc, st);
-    return launch_talking<T, 8, 4>(a, 1, tc_gc, st);
+    if (rep == 1) return launch_talking<T, 1, 4>(a, 1, tc_gc, pv_tc, st);
+    if (rep == 2) return launch_talking<T, 2, 4>(a, 1, tc_gc, pv_tc, st);
+    if (rep <= 4) return launch_talking<T, 4, 4>(a, 1, tc_gc, pv_tc, st);
+    return launch_talking<T, 8, 4>(a, 1, tc_gc, pv_tc, st);
   }
   // one row per CTA: a cluster of four CTAs shares the row's key blocks (the split is fixed, so a token's sums do not depend on
   // what else the batch holds); QSPEC_SEQ_TALK_SPLIT=1 keeps one CTA per row, for comparison
   static const int split = [] { const char* v = getenv("QSPEC_SEQ_TALK_SPLIT"); const int n = v ? atoi(v) : 4; return n >= 1 && n <= 8 ? n : 4; }();
-  if (rep == 1) return launch_talking<T, 1, 1>(a, split, 0, st);
-  if (rep == 2) return launch_talking<T, 2, 1>(a, split, 0, st);
-  if (rep <= 4) return launch_talking<T, 4, 1>(a, split, 0, st);
-  return launch_talking<T, 8, 1>(a, split, 0, st);
+  if (rep == 1) return launch_talking<T, 1, 1>(a, split, 0, 0, st);
+  if (rep == 2) return launch_talking<T, 2, 1>(a, split, 0, 0, st);
+  if (rep <= 4) return launch_talking<T, 4, 1>(a, split, 0, 0, st);
+  return launch_talking<T, 8, 1>(a, split, 0, 0, st);
 }
 
 extern "C" int qspec_seq_talking_attention(const qspec_talking_attn_args* a, int rows_per_cta, int dtype, void* stream) {
