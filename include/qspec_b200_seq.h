@@ -314,7 +314,9 @@ int qspec_seq_gqa_prep(const void* p, int ld, const float* qn_w, const float* kn
  * term); head h applies sum_g talk[h, g] weight_g(j) to the values of its own key/value head h / (H / G). q float32 [ntok, H, D];
  * keys and values as rows of per-slot rings with element strides, as for qspec_seq_window_attention; talk float32 [H, H];
  * out [ntok, H, DV]. rows_per_cta: 4 lets a CTA take four consecutive batch rows, which share every key and value row they
- * read when they belong to one sequence (prompt portions); 1 gives every row a CTA of its own (decode-shaped batches). */
+ * read when they belong to one sequence (prompt portions); 1 gives every row a cluster of CTAs of its own (decode-shaped
+ * batches). With four rows per CTA, bfloat16 caches, head sizes that are multiples of 16 and at most eight heads per key/value
+ * head, the score and value products run on the tensor cores (queries rounded to bfloat16, weights as a two-term split). */
 typedef struct qspec_talking_attn_args {
   const float* q;
   const void* k; long long k_slot_stride; int k_row_stride, k_head_stride;
